@@ -11,7 +11,9 @@ future of a request reserved at admission
 What is different here:
 
 * cache layers are put in **groups** by what they keep (kv_heads, head_dim,
-  window); every group has a pool, an allocator and block tables of its own;
+  window, stride); every group has a pool, an allocator and block tables of its own;
+  a group with a stride s > 1 holds one entry per full run of s tokens (a pooled
+  key and value, say) and takes its pages s times slower than the request grows;
 * pages are taken as tokens arrive (:meth:`CacheManager.extend`), and a group
   with a window gives pages back as soon as the window has passed them
   (:meth:`CacheManager.release_behind_window`), all others when the request ends;
@@ -152,15 +154,19 @@ class CacheManager:
         self._group_of_layer: list[tuple[int, int]] = []      # cache layer -> (group, index in group)
         by_spec: dict[CacheSpec, int] = {}
         for layer, spec in enumerate(cache_specs):
+            if spec.stride < 1:
+                raise ValueError("a cache's stride is at least 1")
             if spec not in by_spec:
                 by_spec[spec] = len(self.groups)
-                self.groups.append(CacheGroup(spec, [], PageAllocator(num_pages), None, None))
+                # (a strided group holds at most tokens / stride entries, and one part-filled page per request)
+                pages = num_pages if spec.stride == 1 else min(num_pages, -(-num_pages // spec.stride) + max_requests)
+                self.groups.append(CacheGroup(spec, [], PageAllocator(pages), None, None))
             group = self.groups[by_spec[spec]]
             self._group_of_layer.append((by_spec[spec], len(group.cache_layers)))
             group.cache_layers.append(layer)
         for group in self.groups:
             if allocate_tensors:
-                shape = (len(group.cache_layers), num_pages, page_size * group.spec.elements_per_token)
+                shape = (len(group.cache_layers), group.allocator.num_pages, page_size * group.spec.elements_per_token)
                 group.pool = torch.zeros(shape, dtype=dtype, device=self.device)
                 group.table_device = torch.full((max_requests, self.max_pages_per_request), -1,
                                                 dtype=torch.int32, device=self.device)
@@ -252,8 +258,8 @@ class CacheManager:
         else:
             have = [0 for _ in self.groups]
             length = length or 0
-        need_total = -(-(length + n_tokens) // self.page_size)
-        return [max(0, need_total - h) for h in have]
+        total = length + n_tokens
+        return [max(0, -(-(total // g.spec.stride) // self.page_size) - h) for g, h in zip(self.groups, have)]
 
     def can_extend(self, request_id: Hashable | None, n_tokens: int, length: int | None = None) -> bool:
         needed = self.pages_needed(request_id, n_tokens, length)
@@ -344,7 +350,7 @@ class CacheManager:
         keys = pages[:, :key_elems].unflatten(1, (spec.kv_heads, page, spec.head_dim))
         values = pages[:, key_elems:].unflatten(1, (spec.kv_heads, page, spec.value_width)) if spec.value_width else None
         if spec.value_width == spec.head_dim:
-            pages = pages.view(self.num_pages, 2, spec.kv_heads, page, spec.head_dim)
+            pages = pages.view(group.allocator.num_pages, 2, spec.kv_heads, page, spec.head_dim)
         return GroupBinding(pages, group.table_device, page, spec.window, keys, values)
 
     def group_of_layer(self, cache_layer: int) -> int:

@@ -111,6 +111,14 @@ __global__ void scale_kernel(float* __restrict__ x, float s, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] *= s;
 }
 
+// x <- cap * tanh(x / cap) (fp32), element by element
+__global__ void softcap_kernel(float* __restrict__ x, float cap, int64_t n) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
 // out[t] = [x[t] ; y[t]] in the activation type (x, y fp32 rows of `width`)
 __global__ void pair_rows_kernel(const float* __restrict__ x, const float* __restrict__ y, void* __restrict__ out,
                                  int out_dtype, int width) {
@@ -217,6 +225,14 @@ TIB_API int tib_scale_f32(float* x, float s, int64_t n, cudaStream_t stream) {
   if (!x || n < 0) return TIB_E_ARG;
   const int blocks = (int)(ceil_div64(n, 256) < 148 * 8 ? ceil_div64(n, 256) : 148 * 8);
   TIB_LAUNCH_DEPENDENT(scale_kernel, blocks, 256, 0, stream, x, s, n);
+  return TIB_OK;
+}
+
+TIB_API int tib_softcap_f32(float* x, float cap, int64_t n, cudaStream_t stream) {
+  if (n == 0) return TIB_OK;
+  if (!x || n < 0 || !(cap > 0.f)) return TIB_E_ARG;
+  const int blocks = (int)(ceil_div64(n, 256) < 148 * 8 ? ceil_div64(n, 256) : 148 * 8);
+  TIB_LAUNCH_DEPENDENT(softcap_kernel, blocks, 256, 0, stream, x, cap, n);
   return TIB_OK;
 }
 

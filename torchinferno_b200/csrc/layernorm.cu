@@ -9,7 +9,7 @@
 //
 //   layernorm          out[i] = LN(x[rows ? rows[i] : i])                   x: fp32 residual or activation rows
 //   layernorm_tail     what follows a sublayer, as one launch, each step optional:
-//                        residual[i] += LN_a(y[i])
+//                        residual[i] += LN_a(y[i])                          (without a norm a: residual[i] += y[i])
 //                        next[i] = sum_{j < count} coef[j] * history[j][i], written to history[count][i], where
 //                                  history[count - 1] is the residual (the running layer's stream)
 //                        out[i] = LN_b(the row at hand)
@@ -43,7 +43,7 @@ __device__ __forceinline__ void ln_stats(const float* row, int width, float eps,
 }
 
 struct LnTail {
-  // residual[i] += LN(y[i]; wa, ba)      (y null: skipped)
+  // residual[i] += LN(y[i]; wa, ba)      (y null: skipped; wa null: residual[i] += y[i])
   const void* y; int y_dtype; int64_t ldy; const float* wa; const float* ba;
   float* residual;                       // [n, width] fp32 (for the depth average: history[count - 1])
   // next = sum_j coef[j] history[j]     (history null: skipped, next = residual)
@@ -64,9 +64,9 @@ __global__ void __launch_bounds__(256) layernorm_tail_kernel(LnTail a) {
   if (a.y) {
     for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = ln_load(a.y, a.y_dtype, i * a.ldy + c);
     __syncthreads();
-    ln_stats(row, width, a.eps, scratch, mean, inv);
+    if (a.wa) ln_stats(row, width, a.eps, scratch, mean, inv);
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float v = a.residual[i * width + c] + ((row[c] - mean) * inv * a.wa[c] + a.ba[c]);
+      const float v = a.residual[i * width + c] + (a.wa ? (row[c] - mean) * inv * a.wa[c] + a.ba[c] : row[c]);
       a.residual[i * width + c] = v;
       row[c] = v;
     }
@@ -158,12 +158,17 @@ __global__ void __launch_bounds__(256) layernorm_tail_vec_kernel(LnTail a, const
         y[p] = make_float4(lo.x, lo.y, hi.x, hi.y);
       }
     }
-    stats(y, mean, inv);
+    if (a.wa) stats(y, mean, inv);
     float4* out4 = reinterpret_cast<float4*>(a.residual + i * width);
 #pragma unroll
     for (int p = 0; p < PER; ++p) {
       const int idx = p * T + tid;
       if (idx >= nvec) continue;
+      if (!a.wa) {
+        r[p].x += y[p].x; r[p].y += y[p].y; r[p].z += y[p].z; r[p].w += y[p].w;
+        out4[idx] = r[p];
+        continue;
+      }
       const float4 w = reinterpret_cast<const float4*>(a.wa)[idx], b = reinterpret_cast<const float4*>(a.ba)[idx];
       r[p].x += (y[p].x - mean) * inv * w.x + b.x;
       r[p].y += (y[p].y - mean) * inv * w.y + b.y;
@@ -268,7 +273,7 @@ TIB_API int tib_layernorm_tail(const void* y, int y_dtype, int64_t ldy, const fl
                                void* out, int out_dtype, int n, int width, float eps, cudaStream_t stream) {
   if (n == 0) return TIB_OK;
   if (!residual || n < 0 || width < 1) return TIB_E_ARG;
-  if (y && (!wa || !ba)) return TIB_E_ARG;
+  if (y && ((wa == nullptr) != (ba == nullptr))) return TIB_E_ARG;
   if (out && (!wb || !bb)) return TIB_E_ARG;
   if (history && (!coef || count < 1 || residual != history + (size_t)(count - 1) * slice)) return TIB_E_ARG;
   if (width > kLnMaxWidth) return TIB_E_SIZE;

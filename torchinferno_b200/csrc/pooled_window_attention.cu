@@ -1,0 +1,468 @@
+// Attention over a sliding window plus one averaged key and value for every block of tokens that lies wholly behind
+// the window, with values that are rotated by their own position.
+//
+//   rotary_kv_append   q, k (+ bias) get the rotary encoding on the first rot_dim elements of a head (pairs i, i + rot/2;
+//                      angle = position * freq[i]; cos and sin times `amplitude`); v (+ bias) is turned over its whole
+//                      width (pairs m, m + vdim/2; angle = position * vfreq[m]); q goes to q_out, k and v into the pages
+//   pool_blocks        for every token that completes a block of `pool` positions (position % pool == pool - 1): the
+//                      mean of the block's cached keys and of its cached values goes into entry position / pool of the
+//                      second, strided cache (sums in fp32, in rising order of position)
+//   attention          query i sees the tokens j with 0 <= i - j < window, and the blocks b with
+//                      b * pool + pool - 1 <= i - window; score = q . k * scale * temp[h]; one softmax over both, with
+//                      exp(sink[h]) added to its denominator; the head's sum of values is turned back by -i over the
+//                      value pairs and multiplied element by element by sigmoid(gate)
+//
+// Scores, the softmax, the sums over values, the turning back and the gate are fp32.  One warp owns one (query token,
+// query head) row from start to end and walks first the blocks, then the tokens, 32 at a time, aligned to absolute
+// block numbers / positions, in rising order: a row's arithmetic depends only on its own position, never on how the
+// batch was cut, which rows share the thread block, or which pages hold the keys.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace tib {
+
+struct PwaCache {
+  void* keys; void* values;          // first key / value of the layer's first page
+  const int* block_table; int table_stride;
+  int page_size; int64_t page_stride; int num_pages;
+};
+
+__device__ __forceinline__ int pwa_page(const PwaCache& c, const int* table, int index, int* error_word, int code) {
+  const int page = table[index / c.page_size];
+  if (page >= 0 && page < c.num_pages) return page;
+  if (error_word) atomicExch(error_word, code);
+  return -1;
+}
+
+// ---------------------------------------------------------------------------------------------------- append
+struct PwaAppendArgs {
+  int64_t ld; int q_off, k_off, v_off;
+  const float* q_bias; const float* k_bias; const float* v_bias;     // [heads * dim], [kv_heads * dim], [kv_heads * vdim] or null
+  const int* positions; const int* token_slot;
+  const float* freq; const float* vfreq;                             // [rot_dim / 2], [vdim / 2] (null: values are not turned)
+  float amplitude;
+  int heads, kv_heads, dim, vdim, rot_dim;
+  PwaCache cache;
+  int* error_word;
+};
+
+// One block per token; a warp per head (q heads, then k heads, then v heads).
+template <typename T>
+__global__ void __launch_bounds__(512) pwa_append_kernel(const T* __restrict__ proj, T* __restrict__ q_out, PwaAppendArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int pos = a.positions[t];
+  const float fpos = (float)pos;
+  const T* row = proj + (size_t)t * a.ld;
+  int page = -1, in_page = 0;
+  if (a.cache.keys) {
+    const int* table = a.cache.block_table + (size_t)a.token_slot[t] * a.cache.table_stride;
+    page = pwa_page(a.cache, table, pos, a.error_word, 0x30000 + (t & 0xffff));
+    in_page = pos % a.cache.page_size;
+  }
+  const int total = a.heads + 2 * a.kv_heads;
+  for (int head = warp; head < total; head += nwarps) {
+    if (head < a.heads + a.kv_heads) {       // a query or key head: partial rotary, pairs (i, i + rot/2)
+      const bool is_q = head < a.heads;
+      const int hh = is_q ? head : head - a.heads;
+      const T* src = row + (is_q ? a.q_off : a.k_off) + hh * a.dim;
+      const float* bias = is_q ? a.q_bias : a.k_bias;
+      T* dst;
+      if (is_q) dst = q_out + (size_t)t * a.heads * a.dim + hh * a.dim;
+      else {
+        if (page < 0) continue;
+        dst = reinterpret_cast<T*>(a.cache.keys) + (size_t)page * a.cache.page_stride + ((size_t)hh * a.cache.page_size + in_page) * a.dim;
+      }
+      const int half = a.rot_dim / 2;
+      for (int i = lane; i < half; i += 32) {
+        float lo = to_f32(src[i]), hi = to_f32(src[i + half]);
+        if (bias) { lo += bias[hh * a.dim + i]; hi += bias[hh * a.dim + i + half]; }
+        const float angle = fpos * a.freq[i];
+        const float c = cosf(angle) * a.amplitude, s = sinf(angle) * a.amplitude;
+        dst[i] = from_f32<T>(rope_lo(lo, hi, c, s));
+        dst[i + half] = from_f32<T>(rope_hi(lo, hi, c, s));
+      }
+      for (int i = a.rot_dim + lane; i < a.dim; i += 32) {
+        float v = to_f32(src[i]);
+        if (bias) v += bias[hh * a.dim + i];
+        dst[i] = from_f32<T>(v);
+      }
+    } else {                                  // a value head: turned over its whole width
+      if (page < 0) continue;
+      const int hh = head - a.heads - a.kv_heads;
+      const T* src = row + a.v_off + hh * a.vdim;
+      T* dst = reinterpret_cast<T*>(a.cache.values) + (size_t)page * a.cache.page_stride + ((size_t)hh * a.cache.page_size + in_page) * a.vdim;
+      if (a.vfreq) {
+        const int half = a.vdim / 2;
+        for (int i = lane; i < half; i += 32) {
+          float lo = to_f32(src[i]), hi = to_f32(src[i + half]);
+          if (a.v_bias) { lo += a.v_bias[hh * a.vdim + i]; hi += a.v_bias[hh * a.vdim + i + half]; }
+          const float angle = fpos * a.vfreq[i];
+          const float c = cosf(angle), s = sinf(angle);
+          dst[i] = from_f32<T>(rope_lo(lo, hi, c, s));
+          dst[i + half] = from_f32<T>(rope_hi(lo, hi, c, s));
+        }
+      } else {
+        for (int i = lane; i < a.vdim; i += 32) {
+          float v = to_f32(src[i]);
+          if (a.v_bias) v += a.v_bias[hh * a.vdim + i];
+          dst[i] = from_f32<T>(v);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ block means
+struct PwaPoolArgs {
+  const int* positions; const int* token_slot;
+  int kv_heads, dim, vdim, pool;
+  PwaCache tokens, blocks;
+  int* error_word;
+};
+
+// grid (tokens, kv_heads); a block has work only where its token completes a block of `pool` positions
+template <typename T>
+__global__ void __launch_bounds__(128) pwa_pool_kernel(PwaPoolArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int pos = a.positions[t];
+  if (pos % a.pool != a.pool - 1) return;
+  const int b = pos / a.pool, first = b * a.pool, slot = a.token_slot[t];
+  const int* ttable = a.tokens.block_table + (size_t)slot * a.tokens.table_stride;
+  const int* btable = a.blocks.block_table + (size_t)slot * a.blocks.table_stride;
+  const int bpage = pwa_page(a.blocks, btable, b, a.error_word, 0x40000 + (t & 0xffff));
+  if (bpage < 0) return;
+  const int width = a.dim + a.vdim;
+  const float inv = 1.f / (float)a.pool;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    const bool is_k = e < a.dim;
+    const int dd = is_k ? e : e - a.dim, w = is_k ? a.dim : a.vdim;
+    const T* base = reinterpret_cast<const T*>(is_k ? a.tokens.keys : a.tokens.values);
+    float sum = 0.f;
+    for (int j = 0; j < a.pool; ++j) {
+      const int page = pwa_page(a.tokens, ttable, first + j, a.error_word, 0x50000 + (t & 0xffff));
+      if (page < 0) continue;
+      sum += to_f32(base[(size_t)page * a.tokens.page_stride + ((size_t)kvh * a.tokens.page_size + (first + j) % a.tokens.page_size) * w + dd]);
+    }
+    T* out = reinterpret_cast<T*>(is_k ? a.blocks.keys : a.blocks.values);
+    out[(size_t)bpage * a.blocks.page_stride + ((size_t)kvh * a.blocks.page_size + b % a.blocks.page_size) * w + dd] = from_f32<T>(sum * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------- attention
+constexpr int kPwaWarps = 4;
+constexpr int kPwaRowsPerWarp = 4;
+constexpr int kPwaRows = kPwaWarps * kPwaRowsPerWarp;      // rows (token, head) per block
+constexpr int kPwaKeys = 32;                               // keys per step = lanes
+
+struct PwaArgs {
+  const int* q_start; const int* kv_start; const int* slots;
+  int heads, kv_heads, dim, vdim;
+  int window, pool;                  // pool 0: no blocks, only the window
+  float scale;
+  const float* temp; const float* sink;                    // [heads] or null
+  const float* vfreq;                                      // [vdim / 2] or null (values were not turned)
+  const void* gate; int gate_dtype; int64_t ld_gate;       // [tokens, heads * vdim] logits or null
+  PwaCache tokens, blocks;
+  int group_chunk, q_tile;
+  int* error_word;
+};
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(kPwaWarps * 32)
+pwa_attention_kernel(const T* __restrict__ q, T* __restrict__ out, PwaArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float smem[];
+  const int d = a.dim, dv = a.vdim;
+  float* q_s = smem;                             // [kPwaRows][d]
+  float* k_s = q_s + kPwaRows * d;               // [32][d + 1]
+  float* v_s = k_s + kPwaKeys * (d + 1);         // [32][dv]
+  float* o_s = v_s + kPwaKeys * dv;              // [kPwaWarps][dv]: a row's sum, for the turning back
+
+  const int entry = blockIdx.y;
+  const int group = a.heads / a.kv_heads;
+  const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
+  const int kvh = blockIdx.z / chunks;
+  const int g0 = (blockIdx.z - kvh * chunks) * a.group_chunk;
+  const int gc = min(a.group_chunk, group - g0);
+
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int t0 = blockIdx.x * a.q_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(a.q_tile, q_len - t0);
+  const int nrows = nt * gc;
+  const int pos0 = a.kv_start[entry] + t0;       // position of the first query of the tile
+  const int last_pos = pos0 + nt - 1;
+  const int slot = a.slots[entry];
+  const int* ttable = a.tokens.block_table + (size_t)slot * a.tokens.table_stride;
+  const int* btable = a.pool > 0 ? a.blocks.block_table + (size_t)slot * a.blocks.table_stride : nullptr;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_width = a.heads * d, o_width = a.heads * dv;
+
+  for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) {
+    const int r = e / d, dd = e - r * d;
+    const int t = r / gc, g = r - t * gc;
+    q_s[r * d + dd] = to_f32(q[(size_t)(row0 + t0 + t) * q_width + (kvh * group + g0 + g) * d + dd]);
+  }
+
+  float m[kPwaRowsPerWarp], l[kPwaRowsPerWarp], acc[kPwaRowsPerWarp][DPL], factor[kPwaRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kPwaRowsPerWarp; ++i) {
+    m[i] = -CUDART_INF_F;
+    l[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) acc[i][j] = 0.f;
+    const int r = warp * kPwaRowsPerWarp + i;
+    const int head = kvh * group + g0 + (r < nrows ? r % gc : 0);
+    factor[i] = a.scale * (a.temp ? a.temp[head] : 1.f);
+  }
+
+  // how many blocks the last query of the tile sees, and the first token any query of the tile sees
+  const int n_blocks = a.pool > 0 ? max(0, last_pos - a.window + 1) / a.pool : 0;
+  const int first_key = max(0, pos0 - a.window + 1);
+  const int steps_b = (n_blocks + kPwaKeys - 1) / kPwaKeys;
+  const int s_lo = first_key / kPwaKeys, s_hi = last_pos / kPwaKeys;
+
+  for (int step = 0; step < steps_b + (s_hi - s_lo + 1); ++step) {
+    const bool pooled = step < steps_b;
+    const int base = pooled ? step * kPwaKeys : (s_lo + step - steps_b) * kPwaKeys;      // first block / position of the step
+    const PwaCache& c = pooled ? a.blocks : a.tokens;
+    const int* table = pooled ? btable : ttable;
+    __syncthreads();      // the tiles of the step before are no longer read (and q_s is written)
+    // Keys outside what the tile can see are zeros and always masked (unwritten cache may hold anything).
+    for (int e = threadIdx.x; e < kPwaKeys * (d + dv); e += blockDim.x) {
+      const int j = e / (d + dv), dd = e - j * (d + dv);
+      const int idx = base + j;
+      const bool wanted = pooled ? idx < n_blocks : (idx <= last_pos && idx >= first_key);
+      float val = 0.f;
+      if (wanted) {
+        const int page = pwa_page(c, table, idx, a.error_word, 0x10000 + entry);
+        if (page >= 0) {
+          const size_t at = (size_t)page * c.page_stride + ((size_t)kvh * c.page_size + idx % c.page_size) * (dd < d ? d : dv);
+          val = dd < d ? to_f32(reinterpret_cast<const T*>(c.keys)[at + dd]) : to_f32(reinterpret_cast<const T*>(c.values)[at + dd - d]);
+        }
+      }
+      if (dd < d) k_s[j * (d + 1) + dd] = val;
+      else v_s[j * dv + dd - d] = val;
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int i = 0; i < kPwaRowsPerWarp; ++i) {
+      const int r = warp * kPwaRowsPerWarp + i;
+      if (r >= nrows) continue;                       // uniform in the warp
+      const int qpos = pos0 + r / gc;
+      const int idx = base + lane;
+      bool allowed;
+      if (pooled) {
+        const int seen = max(0, qpos - a.window + 1) / a.pool;      // blocks 0 .. seen - 1 lie wholly behind the window
+        if (base >= seen) continue;
+        allowed = idx < seen;
+      } else {
+        const int lo = max(0, qpos - a.window + 1);
+        if (base > qpos || base + kPwaKeys - 1 < lo) continue;
+        allowed = idx <= qpos && idx >= lo;
+      }
+      float s = 0.f;
+      const float* qr = q_s + r * d;
+      const float* kr = k_s + lane * (d + 1);
+      for (int dd = 0; dd < d; ++dd) s = fmaf(qr[dd], kr[dd], s);
+      s = allowed ? s * factor[i] : -CUDART_INF_F;
+      const float m_new = fmaxf(m[i], warp_max(s));   // finite: the step holds a key the row sees
+      const float alpha = m[i] == -CUDART_INF_F ? 0.f : expf(m[i] - m_new);
+      const float p = allowed ? expf(s - m_new) : 0.f;
+      l[i] = l[i] * alpha + warp_sum(p);
+      m[i] = m_new;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) acc[i][j] *= alpha;
+      for (int kk = 0; kk < kPwaKeys; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, p, kk);
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) {
+          const int dd = lane + 32 * j;
+          if (dd < dv) acc[i][j] = fmaf(pk, v_s[kk * dv + dd], acc[i][j]);
+        }
+      }
+    }
+  }
+
+  float* o_row = o_s + warp * dv;
+#pragma unroll
+  for (int i = 0; i < kPwaRowsPerWarp; ++i) {
+    const int r = warp * kPwaRowsPerWarp + i;
+    if (r >= nrows) continue;
+    const int t = r / gc, g = r - t * gc;
+    const int head = kvh * group + g0 + g;
+    const size_t token = (size_t)(row0 + t0 + t);
+    // the number in the denominator has no key: it only takes weight away from the others
+    float top = m[i], denom = l[i];
+    if (a.sink) {
+      const float sink = a.sink[head];
+      top = fmaxf(m[i], sink);
+      denom = l[i] * expf(m[i] - top) + expf(sink - top);
+    }
+    const float inv = expf(m[i] - top) / denom;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      const int dd = lane + 32 * j;
+      if (dd < dv) o_row[dd] = acc[i][j] * inv;
+    }
+    __syncwarp();
+    T* dst = out + token * o_width + head * dv;
+    const float fpos = (float)(pos0 + t);
+    const int half = dv / 2;
+    for (int mm = lane; mm < (a.vfreq ? half : dv); mm += 32) {
+      if (a.vfreq) {
+        // turn the pair (mm, mm + half) back by the query's position: (u, v) -> (u cos + v sin, v cos - u sin)
+        const float angle = fpos * a.vfreq[mm];
+        const float c = cosf(angle), s = sinf(angle);
+        float u = rope_lo(o_row[mm], o_row[mm + half], c, -s), v = rope_hi(o_row[mm], o_row[mm + half], c, -s);
+        if (a.gate) {
+          const float gu = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * dv + mm]
+                                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[token * a.ld_gate + head * dv + mm]);
+          const float gv = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * dv + mm + half]
+                                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[token * a.ld_gate + head * dv + mm + half]);
+          u *= 1.f / (1.f + expf(-gu));
+          v *= 1.f / (1.f + expf(-gv));
+        }
+        dst[mm] = from_f32<T>(u);
+        dst[mm + half] = from_f32<T>(v);
+      } else {
+        float u = o_row[mm];
+        if (a.gate) {
+          const float gu = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * dv + mm]
+                                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[token * a.ld_gate + head * dv + mm]);
+          u *= 1.f / (1.f + expf(-gu));
+        }
+        dst[mm] = from_f32<T>(u);
+      }
+    }
+  }
+}
+
+template <typename T, int DPL>
+static int pwa_launch(const void* q, void* out, const PwaArgs& a, int n_entries, int max_q_len, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)kPwaRows * a.dim + (size_t)kPwaKeys * (a.dim + 1) + (size_t)kPwaKeys * a.vdim +
+                                       (size_t)kPwaWarps * a.vdim);
+  if (smem > 227 * 1024) return TIB_E_SMEM;
+  auto kern = pwa_attention_kernel<T, DPL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int group = a.heads / a.kv_heads;
+  const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
+  const dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, a.kv_heads * chunks);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kPwaWarps * 32, smem, stream, (const T*)q, (T*)out, a);
+  return TIB_OK;
+}
+
+static PwaCache pwa_cache(void* keys, void* values, const int* table, int table_stride, int page_size, int64_t page_stride, int num_pages) {
+  PwaCache c;
+  c.keys = keys; c.values = values; c.block_table = table; c.table_stride = table_stride; c.page_size = page_size;
+  c.page_stride = page_stride; c.num_pages = num_pages;
+  return c;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// proj: [n_tokens, ld] rows holding q at q_off, k at k_off, v at v_off; q_out: [n_tokens, heads * dim]; k_pages / v_pages:
+// first key / value of this layer's first page (null: only q is made).  Biases, freq and vfreq are fp32.
+TIB_API int tib_rotary_kv_append(const void* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_bias,
+                                 const float* k_bias, const float* v_bias, void* q_out, void* k_pages, void* v_pages,
+                                 const int* positions, const int* token_slot, const int* block_table, int table_stride,
+                                 const float* freq, const float* vfreq, float amplitude, int n_tokens, int heads, int kv_heads,
+                                 int dim, int vdim, int rot_dim, int page_size, int64_t page_stride, int num_pages, int* error_word,
+                                 int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return TIB_OK;
+  if (!proj || !q_out || !positions || n_tokens < 0 || heads < 1 || kv_heads < 1 || dim < 1 || vdim < 1) return TIB_E_ARG;
+  if (rot_dim < 0 || rot_dim % 2 || rot_dim > dim || (rot_dim > 0 && !freq) || (vfreq && vdim % 2)) return TIB_E_SIZE;
+  if (k_pages && (!v_pages || !token_slot || !block_table || page_size < 1)) return TIB_E_ARG;
+  PwaAppendArgs a;
+  a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.q_bias = q_bias; a.k_bias = k_bias; a.v_bias = v_bias;
+  a.positions = positions; a.token_slot = token_slot; a.freq = freq; a.vfreq = vfreq; a.amplitude = amplitude;
+  a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.rot_dim = rot_dim;
+  a.cache = pwa_cache(k_pages, v_pages, block_table, table_stride, page_size, page_stride, num_pages);
+  a.error_word = error_word;
+  const int total = heads + 2 * kv_heads;
+  const int threads = 32 * (total < 4 ? 4 : total > 16 ? 16 : total);
+  if (dtype == TIB_F32)
+    TIB_LAUNCH_DEPENDENT(pwa_append_kernel<float>, n_tokens, threads, 0, stream, (const float*)proj, (float*)q_out, a);
+  else if (dtype == TIB_BF16)
+    TIB_LAUNCH_DEPENDENT(pwa_append_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)proj,
+                         (__nv_bfloat16*)q_out, a);
+  else
+    return TIB_E_DTYPE;
+  return TIB_OK;
+}
+
+// The means of the blocks of `pool` positions that the step's tokens complete, from the token pages (k_pages, v_pages,
+// block_table ...) into the strided pages (bk_pages, bv_pages, b_table ...), whose entry b stands for block b.
+TIB_API int tib_pool_blocks(const void* k_pages, const void* v_pages, const int* block_table, int table_stride, int page_size,
+                            int64_t page_stride, int num_pages, void* bk_pages, void* bv_pages, const int* b_table,
+                            int b_table_stride, int b_page_size, int64_t b_page_stride, int b_num_pages, const int* positions,
+                            const int* token_slot, int n_tokens, int kv_heads, int dim, int vdim, int pool, int* error_word,
+                            int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return TIB_OK;
+  if (!k_pages || !v_pages || !block_table || !bk_pages || !bv_pages || !b_table || !positions || !token_slot) return TIB_E_ARG;
+  if (kv_heads < 1 || kv_heads > 65535 || dim < 1 || vdim < 1 || pool < 1 || page_size < 1 || b_page_size < 1) return TIB_E_SIZE;
+  PwaPoolArgs a;
+  a.positions = positions; a.token_slot = token_slot; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.pool = pool;
+  a.tokens = pwa_cache(const_cast<void*>(k_pages), const_cast<void*>(v_pages), block_table, table_stride, page_size, page_stride, num_pages);
+  a.blocks = pwa_cache(bk_pages, bv_pages, b_table, b_table_stride, b_page_size, b_page_stride, b_num_pages);
+  a.error_word = error_word;
+  const dim3 grid(n_tokens, kv_heads);
+  if (dtype == TIB_F32) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<float>, grid, 128, 0, stream, a);
+  else if (dtype == TIB_BF16) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<__nv_bfloat16>, grid, 128, 0, stream, a);
+  else return TIB_E_DTYPE;
+  return TIB_OK;
+}
+
+// q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, heads * vdim] logits (row stride ld_gate, its
+// own dtype) or null; temp, sink: [heads] fp32 or null; vfreq: [vdim / 2] fp32 or null.  pool 0: the window alone.
+TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_start, const int* kv_start, const int* slots,
+                                        const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
+                                        int page_size, int64_t page_stride, int num_pages, const void* bk_pages,
+                                        const void* bv_pages, const int* b_table, int b_table_stride, int b_page_size,
+                                        int64_t b_page_stride, int b_num_pages, int n_entries, int max_q_len, int heads,
+                                        int kv_heads, int dim, int vdim, int window, int pool, float scale, const float* temp,
+                                        const float* sink, const float* vfreq, const void* gate, int gate_dtype, int64_t ld_gate,
+                                        int* error_word, int dtype, cudaStream_t stream) {
+  if (n_entries == 0 || max_q_len == 0) return TIB_OK;
+  if (!q || !out || !q_start || !kv_start || !slots || !k_pages || !v_pages || !block_table) return TIB_E_ARG;
+  if (pool > 0 && (!bk_pages || !bv_pages || !b_table || b_page_size < 1)) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || vdim < 1 || page_size < 1 || window < 1 || pool < 0) return TIB_E_SIZE;
+  if (dim > 256 || vdim > 256 || (vfreq && vdim % 2) || n_entries > 65535) return TIB_E_SIZE;
+  if (gate && gate_dtype != TIB_F32 && gate_dtype != TIB_BF16) return TIB_E_DTYPE;
+  PwaArgs a;
+  a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim;
+  a.window = window; a.pool = pool; a.scale = scale; a.temp = temp; a.sink = sink; a.vfreq = vfreq; a.gate = gate;
+  a.gate_dtype = gate_dtype; a.ld_gate = ld_gate;
+  a.tokens = pwa_cache(const_cast<void*>(k_pages), const_cast<void*>(v_pages), block_table, table_stride, page_size, page_stride, num_pages);
+  a.blocks = pwa_cache(const_cast<void*>(bk_pages), const_cast<void*>(bv_pages), b_table, b_table_stride, b_page_size, b_page_stride, b_num_pages);
+  a.error_word = error_word;
+  const int group = heads / kv_heads;
+  a.group_chunk = group < kPwaRows ? group : kPwaRows;
+  a.q_tile = kPwaRows / a.group_chunk;
+  const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
+  if ((int64_t)kv_heads * chunks > 65535) return TIB_E_SIZE;
+  const int dpl = (vdim + 31) / 32;
+#define TIB_PWA_DISPATCH(T)                                                              \
+  (dpl <= 1 ? pwa_launch<T, 1>(q, out, a, n_entries, max_q_len, stream)                  \
+   : dpl <= 2 ? pwa_launch<T, 2>(q, out, a, n_entries, max_q_len, stream)                \
+   : dpl <= 4 ? pwa_launch<T, 4>(q, out, a, n_entries, max_q_len, stream)                \
+              : pwa_launch<T, 8>(q, out, a, n_entries, max_q_len, stream))
+  if (dtype == TIB_F32) return TIB_PWA_DISPATCH(float);
+  if (dtype == TIB_BF16) return TIB_PWA_DISPATCH(__nv_bfloat16);
+#undef TIB_PWA_DISPATCH
+  return TIB_E_DTYPE;
+}

@@ -66,7 +66,7 @@ def block_weights(block) -> BlockWeights | None:
     if type(mixer) is not GQAAttention or type(ffn) is not SwiGLUFeedForward or type(n1) is not RMSNorm or type(n2) is not RMSNorm:
         return None
     position = mixer.position
-    if type(position) not in (RotaryEncoding, NoPositionEncoding):
+    if type(position) not in (RotaryEncoding, NoPositionEncoding) or getattr(position, "amplitude", 1.0) != 1.0:
         return None
     if not ops.attention_mma_supports(mixer.head_dim, mixer.heads // mixer.kv_heads):
         return None

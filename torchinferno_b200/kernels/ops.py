@@ -124,7 +124,9 @@ def lib() -> ctypes.CDLL:
                    "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
                    "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group", "tib_router_logits",
                    "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
-                   "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence"):
+                   "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence",
+                   "tib_softcap_f32", "tib_short_conv", "tib_ssd_scan", "tib_ssd_scan_max_state", "tib_gated_group_norm",
+                   "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -1046,7 +1048,8 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: fl
 def layernorm_tail(residual: torch.Tensor, eps: float, *, y: torch.Tensor | None = None, y_norm: tuple | None = None,
                    history: torch.Tensor | None = None, coef: torch.Tensor | None = None, count: int = 0,
                    out: torch.Tensor | None = None, out_norm: tuple | None = None) -> None:
-    """What follows a sublayer, in one launch: ``residual += LN(y; *y_norm)`` (if ``y``); then, if ``history``
+    """What follows a sublayer, in one launch: ``residual += LN(y; *y_norm)`` (if ``y``; with ``y_norm`` None: ``residual
+    += y``); then, if ``history``
     ([depth, n, width] fp32 whose slice ``count - 1`` is ``residual``), ``history[count] = sum_j coef[j] * history[j]``
     over j < count; then, if ``out``, ``out = LN(the row at hand; *out_norm)``.  Norms are (weight, bias) in fp32."""
     _need(residual, "residual", torch.float32)
@@ -1054,9 +1057,12 @@ def layernorm_tail(residual: torch.Tensor, eps: float, *, y: torch.Tensor | None
     wa = ba = wb = bb = None
     if y is not None:
         _rows_of(y, "y", width)
-        wa, ba = y_norm
-        if y.shape[0] != n or wa.numel() != width or ba.numel() != width or wa.dtype != torch.float32 or ba.dtype != torch.float32:
-            raise KernelError("layernorm_tail: y or its norm do not fit")
+        if y.shape[0] != n:
+            raise KernelError("layernorm_tail: y does not fit")
+        if y_norm is not None:
+            wa, ba = y_norm
+            if wa.numel() != width or ba.numel() != width or wa.dtype != torch.float32 or ba.dtype != torch.float32:
+                raise KernelError("layernorm_tail: the norm of y does not fit")
     slice_elems = 0
     if history is not None:
         _need(history, "history", torch.float32), _need(coef, "coef", torch.float32)
@@ -1180,4 +1186,175 @@ def gated_recurrence(proj: torch.Tensor, z_off: int, u_off: int, g_off: int, bia
     _check("gated_recurrence", status)
     if runs > 1:
         count_launches(1)
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) (fp32, in place)."""
+    _need(x, "x", torch.float32)
+    if not cap > 0:
+        raise KernelError("softcap: the cap is positive")
+    _check("softcap", lib().tib_softcap_f32(_ptr(x), c_float(cap), c_int64(x.numel()), _stream()))
+    return x
+
+
+# ---------------------------------------------------------------------------
+# The state-space mixer (csrc/state_space.cu).
+def short_conv(rows: torch.Tensor, col: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, state_off: int,
+               q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_entries: int, max_q_len: int, *,
+               silu: bool = True) -> torch.Tensor:
+    """out[t, c] = act(bias[c] + sum_k weight[c, k] * rows[t - taps + 1 + k, col + c]), causal within each entry of the
+    ragged batch; the taps - 1 inputs before an entry's first token come from ``state[slot, state_off:]`` (laid out
+    [taps - 1, channels]), where the kernel then leaves the entry's last taps - 1 inputs.  act: silu, or the identity."""
+    _rows_of(rows, "rows"), _need(weight, "weight", torch.float32), _need(state, "state", torch.float32), _need(out, "out")
+    channels, taps = weight.shape
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if (out.shape != (rows.shape[0], channels) or col < 0 or col + channels > rows.shape[1] or state.dim() != 2
+            or state_off < 0 or state_off + (taps - 1) * channels > state.shape[1] or (bias is not None and bias.numel() != channels)):
+        raise KernelError("short_conv: shapes do not fit")
+    _check("short_conv", lib().tib_short_conv(
+        _ptr(rows), c_int(_code(rows.dtype)), c_int64(rows.stride(0)), c_int(col), _ptr(weight), _ptr(bias), _ptr(state),
+        c_int64(state.stride(0)), c_int64(state_off), _ptr(q_start), _ptr(slots), _ptr(out), c_int(_code(out.dtype)), c_int(channels),
+        c_int(taps), c_int(int(silu)), c_int(n_entries), c_int(max_q_len), _stream()))
+    return out
+
+
+def ssd_scan_max_state() -> int:
+    return int(lib().tib_ssd_scan_max_state())
+
+
+def ssd_scan(xbc: torch.Tensor, dt_rows: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y: torch.Tensor, n_entries: int, *, heads: int,
+             groups: int, state_dim: int, head_dim: int) -> torch.Tensor:
+    """The recurrence S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t per head over the ragged batch;
+    ``xbc`` rows hold [x | B | C]; ``dt_rows[:, dt_col + h]`` the raw step size of head h; S is the first
+    heads * state_dim * head_dim floats of ``state[slot]`` (fp32), read at the start and left at the end."""
+    _rows_of(xbc, "xbc", heads * head_dim + 2 * groups * state_dim), _rows_of(dt_rows, "dt_rows")
+    _need(state, "state", torch.float32), _need(y, "y", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"ssd_scan: {name} has the wrong length")
+    if (y.shape != (xbc.shape[0], heads * head_dim) or dt_rows.shape[0] != xbc.shape[0] or dt_col < 0
+            or dt_col + heads > dt_rows.shape[1] or state.dim() != 2 or state.shape[1] < heads * state_dim * head_dim):
+        raise KernelError("ssd_scan: shapes do not fit")
+    _check("ssd_scan", lib().tib_ssd_scan(
+        _ptr(xbc), c_int(_code(xbc.dtype)), c_int64(xbc.stride(0)), _ptr(dt_rows), c_int(_code(dt_rows.dtype)),
+        c_int64(dt_rows.stride(0)), c_int(dt_col), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), c_int64(state.stride(0)),
+        _ptr(q_start), _ptr(slots), _ptr(y), c_int(heads), c_int(groups), c_int(state_dim), c_int(head_dim), c_int(n_entries),
+        _stream()))
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, z_rows: torch.Tensor, z_col: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                     parts: int) -> torch.Tensor:
+    """out = v / sqrt(mean(v^2) + eps) * weight with v = y * silu(z) and the mean taken over each of ``parts`` equal runs
+    of the row; y fp32, z = ``z_rows[:, z_col : z_col + width]``."""
+    _need(y, "y", torch.float32), _rows_of(z_rows, "z_rows"), _need(weight, "weight", torch.float32), _need(out, "out")
+    n, width = y.shape
+    if out.shape != y.shape or weight.numel() != width or z_rows.shape[0] != n or z_col < 0 or z_col + width > z_rows.shape[1]:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    _check("gated_group_norm", lib().tib_gated_group_norm(
+        _ptr(y), _ptr(z_rows), c_int(_code(z_rows.dtype)), c_int64(z_rows.stride(0)), c_int(z_col), _ptr(weight), c_float(eps),
+        _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), c_int(parts), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Attention over a window and pooled blocks (csrc/pooled_window_attention.cu).
+def _pages(keys: torch.Tensor, values: torch.Tensor, kv_heads: int, dim: int, vdim: int, name: str) -> tuple[int, int, int]:
+    """(num_pages, page_size, page_stride) of one layer's [pages, kv_heads, page_size, dim / vdim] views."""
+    if (keys.shape[1:] != (kv_heads, keys.shape[2], dim) or values.shape[1:] != (kv_heads, keys.shape[2], vdim)
+            or keys.stride(0) != values.stride(0) or not keys[0].is_contiguous() or not values[0].is_contiguous()
+            or keys.dtype != values.dtype):
+        raise KernelError(f"{name}: keys / values are not one layer's pages")
+    return keys.shape[0], keys.shape[2], keys.stride(0)
+
+
+def rotary_kv_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, keys: torch.Tensor,
+                     values: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor, block_table: torch.Tensor,
+                     freq: torch.Tensor, value_freq: torch.Tensor | None, heads: int, kv_heads: int, dim: int, vdim: int, *,
+                     rot_dim: int, amplitude: float = 1.0, q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None,
+                     v_bias: torch.Tensor | None = None, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Add the biases, rotate the first ``rot_dim`` elements of every q and k head of the fused projection ``proj`` (pairs i,
+    i + rot_dim / 2, cos and sin times ``amplitude``), turn every v head over its whole width by ``value_freq`` (None: not),
+    write q to ``q_out`` and k, v into their pages."""
+    _rows_of(proj, "proj"), _need(q_out, "q_out", proj.dtype), _need(positions, "positions", torch.int32)
+    _need(token_slot, "token_slot", torch.int32), _need(block_table, "block_table", torch.int32), _need(freq, "freq", torch.float32)
+    n = proj.shape[0]
+    if q_out.shape != (n, heads * dim) or keys.dtype != proj.dtype or freq.numel() * 2 != rot_dim:
+        raise KernelError("rotary_kv_append: shapes or types do not fit")
+    for t, width in ((q_bias, heads * dim), (k_bias, kv_heads * dim), (v_bias, kv_heads * vdim)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous()):
+            raise KernelError("rotary_kv_append: a bias does not fit")
+    if value_freq is not None and (value_freq.dtype != torch.float32 or value_freq.numel() * 2 != vdim):
+        raise KernelError("rotary_kv_append: value_freq does not fit")
+    num_pages, page_size, page_stride = _pages(keys, values, kv_heads, dim, vdim, "rotary_kv_append")
+    _check("rotary_kv_append", lib().tib_rotary_kv_append(
+        _ptr(proj), c_int64(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+        _ptr(q_out), _ptr(keys), _ptr(values), _ptr(positions), _ptr(token_slot), _ptr(block_table), c_int(block_table.stride(0)),
+        _ptr(freq), _ptr(value_freq), c_float(amplitude), c_int(n), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+        c_int(rot_dim), c_int(page_size), c_int64(page_stride), c_int(num_pages), _ptr(error_word), c_int(_code(proj.dtype)), _stream()))
+    return q_out
+
+
+def pool_blocks(keys: torch.Tensor, values: torch.Tensor, block_table: torch.Tensor, block_keys: torch.Tensor,
+                block_values: torch.Tensor, block_block_table: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor,
+                pool: int, *, error_word: torch.Tensor | None = None) -> None:
+    """For every token of the step that completes a block of ``pool`` positions, the mean of the block's cached keys and of
+    its cached values goes into entry position // pool of the strided pages ``block_keys`` / ``block_values``."""
+    kv_heads, dim, vdim = keys.shape[1], keys.shape[3], values.shape[3]
+    num_pages, page_size, page_stride = _pages(keys, values, kv_heads, dim, vdim, "pool_blocks")
+    b_pages, b_page_size, b_stride = _pages(block_keys, block_values, kv_heads, dim, vdim, "pool_blocks")
+    if block_keys.dtype != keys.dtype:
+        raise KernelError("pool_blocks: the two caches differ in type")
+    _need(positions, "positions", torch.int32), _need(token_slot, "token_slot", torch.int32)
+    _check("pool_blocks", lib().tib_pool_blocks(
+        _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size), c_int64(page_stride),
+        c_int(num_pages), _ptr(block_keys), _ptr(block_values), _ptr(block_block_table), c_int(block_block_table.stride(0)),
+        c_int(b_page_size), c_int64(b_stride), c_int(b_pages), _ptr(positions), _ptr(token_slot), c_int(positions.numel()),
+        c_int(kv_heads), c_int(dim), c_int(vdim), c_int(pool), _ptr(error_word), c_int(_code(keys.dtype)), _stream()))
+
+
+def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor, kv_start: torch.Tensor, slots: torch.Tensor,
+                            keys: torch.Tensor, values: torch.Tensor, block_table: torch.Tensor, block_keys: torch.Tensor | None,
+                            block_values: torch.Tensor | None, block_block_table: torch.Tensor | None, n_entries: int,
+                            max_q_len: int, heads: int, kv_heads: int, *, window: int, pool: int, scale: float,
+                            temp: torch.Tensor | None = None, sink: torch.Tensor | None = None,
+                            value_freq: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                            error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Per head, out[i] = sigmoid(gate[i]) * turn_back_i(sum_j w_ij v_j + sum_b w_ib V_b): softmax weights over the tokens j
+    with 0 <= i - j < window and the blocks b of ``pool`` positions with b * pool + pool - 1 <= i - window (their means K_b,
+    V_b from the strided pages), scores q . k * scale * temp[h], exp(sink[h]) added to the denominator; turn_back undoes at
+    position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone."""
+    _need(q, "q"), _need(out, "out", q.dtype)
+    dim, vdim = keys.shape[3], values.shape[3]
+    n = q.shape[0]
+    if q.shape != (n, heads * dim) or out.shape != (n, heads * vdim) or keys.dtype != q.dtype:
+        raise KernelError("pooled_window_attention: shapes or types do not fit")
+    num_pages, page_size, page_stride = _pages(keys, values, kv_heads, dim, vdim, "pooled_window_attention")
+    b_pages = b_page_size = b_stride = b_table_stride = 0
+    if pool > 0:
+        if block_keys is None or block_values is None or block_block_table is None or block_keys.dtype != q.dtype:
+            raise KernelError("pooled_window_attention: blocks need their pages")
+        b_pages, b_page_size, b_stride = _pages(block_keys, block_values, kv_heads, dim, vdim, "pooled_window_attention")
+        b_table_stride = block_block_table.stride(0)
+    for name, t in (("temp", temp), ("sink", sink)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous()):
+            raise KernelError(f"pooled_window_attention: {name} does not fit")
+    if value_freq is not None and (value_freq.dtype != torch.float32 or value_freq.numel() * 2 != vdim):
+        raise KernelError("pooled_window_attention: value_freq does not fit")
+    ld_gate = 0
+    if gate is not None:
+        _rows_of(gate, "gate", heads * vdim)
+        ld_gate = gate.stride(0)
+    _check("pooled_window_attention", lib().tib_pooled_window_attention(
+        _ptr(q), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(keys), _ptr(values), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), c_int64(page_stride), c_int(num_pages),
+        _ptr(block_keys if pool > 0 else None), _ptr(block_values if pool > 0 else None),
+        _ptr(block_block_table if pool > 0 else None), c_int(b_table_stride), c_int(b_page_size), c_int64(b_stride), c_int(b_pages),
+        c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(window), c_int(pool),
+        c_float(scale), _ptr(temp), _ptr(sink), _ptr(value_freq), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
+        c_int64(ld_gate), _ptr(error_word), c_int(_code(q.dtype)), _stream()))
     return out

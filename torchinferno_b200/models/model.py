@@ -123,6 +123,17 @@ class CausalLM:
             if call.cache in needs and needs[call.cache] != cs:
                 raise ValueError(f"cache layer {call.cache} is shared by mixers of different shapes")
             needs.setdefault(call.cache, cs)
+        for call in self.spec.schedule:
+            if isinstance(call, StageCall):
+                continue
+            side = self.blocks[call.layer].mixer.side_cache_spec()
+            if (side is None) != (call.side_cache is None):
+                raise ValueError(f"layer {call.layer}: the mixer's second cache and the schedule's side_cache do not agree")
+            if side is not None:
+                needs[call.side_cache] = side
+        missing = [i for i in range(self.spec.cache_layers) if i not in needs]
+        if missing:
+            raise ValueError(f"cache layers {missing} are used by no layer call")
         return [needs[i] for i in range(self.spec.cache_layers)]
 
     def capturable(self) -> bool:
@@ -170,8 +181,12 @@ class CausalLM:
             if call.cache is not None:
                 kv = cache.kv_binding(call.cache)
                 kv = KVBinding(kv.pool, kv.block_table, kv.page_size, kv.window, call.writes_cache, kv.keys, kv.values)
+            side = None
+            if call.side_cache is not None:
+                b = cache.kv_binding(call.side_cache)
+                side = KVBinding(b.pool, b.block_table, b.page_size, b.window, True, b.keys, b.values)
             ctx = LayerContext(batch=batch, kv=kv, state=cache.state(index),
-                               error_word=cache.error_word, layer_index=index)
+                               error_word=cache.error_word, layer_index=index, side_kv=side)
             self.blocks[call.layer].forward(stream, ctx)
         if batch.n_logits == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -179,4 +194,6 @@ class CausalLM:
         logits = linear(rows, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale != 1.0:
             ops.scale_(logits, self.spec.logit_scale)
+        if self.spec.logit_softcap:
+            ops.softcap_(logits, self.spec.logit_softcap)
         return logits

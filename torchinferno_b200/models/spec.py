@@ -28,6 +28,7 @@ class LayerCall:
     layer: int                      # index into ModelSpec.layers
     cache: int | None = None        # cache layer this call uses (None: the mixer keeps no keys)
     writes_cache: bool = True
+    side_cache: int | None = None   # cache layer of the mixer's second cache (``Mixer.side_cache_spec``), which it writes
 
 
 @dataclass(frozen=True)
@@ -54,6 +55,7 @@ class ModelSpec:
     logit_scale: float = 1.0                  # the head's output is multiplied by this
     keeps_embedding_output: bool = False      # stages read the embedding output (``ResidualStream.origin``)
     embedding_scale: float = 1.0              # the embedding output is multiplied by this
+    logit_softcap: float | None = None        # c > 0: logits <- c * tanh(logits / c), after ``logit_scale``
     history_depth: int = 0                    # > 0: the residual stream lives in a [depth, tokens, hidden] tensor whose
                                               # slice 0 keeps the embedding output and whose later slices keep what
                                               # blocks leave there (``ResidualStream.history``); the stream starts in slice 1
@@ -67,6 +69,10 @@ class ModelSpec:
                 raise ValueError(f"schedule names layer {call.layer}, but there are {len(self.layers)}")
         written: set[int] = set()
         for call in self.schedule:
+            if isinstance(call, LayerCall) and call.side_cache is not None:
+                if call.side_cache in written or call.side_cache == call.cache:
+                    raise ValueError(f"cache layer {call.side_cache} is written by two layer calls")
+                written.add(call.side_cache)
             if isinstance(call, StageCall) or call.cache is None:
                 continue
             if call.writes_cache:
@@ -78,5 +84,6 @@ class ModelSpec:
 
     @property
     def cache_layers(self) -> int:
-        ids = [call.cache for call in self.schedule if isinstance(call, LayerCall) and call.cache is not None]
+        calls = [call for call in self.schedule if isinstance(call, LayerCall)]
+        ids = [c for call in calls for c in (call.cache, call.side_cache) if c is not None]
         return max(ids) + 1 if ids else 0

@@ -14,7 +14,7 @@ Interfaces
 ``Part``           ``weight_specs()``, ``bind(weights)``
 ``Norm``           ``forward(residual, out, rows)`` / ``add_forward(delta, residual, out, rows)``
 ``PositionEncoding`` ``encode_and_store(qkv, q_out, ctx, heads, kv_heads, head_dim)``
-``Mixer``          ``cache_spec()``, ``state_spec()``, ``forward(x, ctx) -> y``
+``Mixer``          ``cache_spec()``, ``side_cache_spec()``, ``state_spec()``, ``forward(x, ctx) -> y``
 ``FeedForward``    ``forward(x, ctx) -> y``
 ``Block``          ``forward(stream, ctx)`` on a :class:`ResidualStream`
 ``StreamStage``    ``forward(stream, ctx)`` between the embedding and the first block
@@ -55,11 +55,16 @@ class CacheSpec:
 
     ``window``: None keeps every token; w > 0 means a query at position p reads
     keys p-w+1 .. p only, so pages wholly behind the window may be given back.
+
+    ``stride``: s > 1 means the cache holds one entry for every full run of s tokens (entry b stands for the
+    positions b*s .. b*s + s - 1 and exists once the last of them has arrived): a summary of the run, such as
+    the mean of its keys.  Such a cache grows s times slower than the request.
     """
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
+    stride: int = 1
 
     @property
     def value_width(self) -> int:
@@ -99,6 +104,7 @@ class LayerContext:
     error_word: torch.Tensor | None = None
     layer_index: int = 0
     call_arg: int = 0                   # the argument of a stage call of the schedule
+    side_kv: KVBinding | None = None    # the second cache of a mixer that keeps one (``Mixer.side_cache_spec``)
 
 
 class ResidualStream:
@@ -192,6 +198,11 @@ class Mixer(Part):
     def cache_spec(self) -> CacheSpec | None:
         return None
 
+    def side_cache_spec(self) -> CacheSpec | None:
+        """A second cache beside the one of :meth:`cache_spec` (``ctx.side_kv``), e.g. one entry per run of tokens
+        (``CacheSpec.stride``) holding a summary of the run."""
+        return None
+
     def state_spec(self) -> StateSpec | None:
         return None
 
@@ -262,4 +273,5 @@ def _ensure_builtin() -> None:
         return
     _loaded = True
     from torchinferno_b200.parts import (attention, block, gated_recurrence, latent_attention, linear_attention, mlp,  # noqa: F401
-                                         moe, norm, parallel_block, rope, sandwich_block, sigmoid_attention, stream_stages)
+                                         moe, norm, parallel_block, pooled_window_attention, rope, sandwich_block,
+                                         sigmoid_attention, state_space, stream_stages)

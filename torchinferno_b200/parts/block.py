@@ -1,7 +1,7 @@
 """The arrangement of parts in one layer.
 
 Pre-norm block (src/torchinferno/models/llama3/pipeline.py:190-198):
-    h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))
+    h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))      (the second line is absent in a layer without a feed-forward)
 The adds are left pending on the residual stream so the next norm (of this
 block, of the next block or the final one) does them in its own pass
 (src/torchinferno/models/llama3/tensor_parallel.py:7430-7435).
@@ -21,28 +21,33 @@ NATIVE_BLOCKS = True          # False: always the part-by-part sequence
 _UNKNOWN = object()
 
 
-def _spec(value: PartSpec | Mapping) -> PartSpec:
-    return value if isinstance(value, PartSpec) else PartSpec(**value)
+def _spec(value: PartSpec | Mapping | None) -> PartSpec | None:
+    return value if value is None or isinstance(value, PartSpec) else PartSpec(**value)
 
 
 class PreNormBlock(Block):
-    def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
-                 feed_forward_norm: PartSpec, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec | None, dtype: torch.dtype, device: torch.device) -> None:
         super().__init__(dtype=dtype, device=device)
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.specs = {"mixer": _spec(mixer), "feed_forward": _spec(feed_forward),
                       "mixer_norm": _spec(mixer_norm), "feed_forward_norm": _spec(feed_forward_norm)}
         self.mixer = build_part("mixer", self.specs["mixer"], dtype=dtype, device=device)
-        self.feed_forward = build_part("feed_forward", self.specs["feed_forward"], dtype=dtype, device=device)
+        self.feed_forward = None if feed_forward is None else \
+            build_part("feed_forward", self.specs["feed_forward"], dtype=dtype, device=device)
         self.mixer_norm = build_part("norm", self.specs["mixer_norm"], dtype=dtype, device=device)
-        self.feed_forward_norm = build_part("norm", self.specs["feed_forward_norm"], dtype=dtype, device=device)
+        self.feed_forward_norm = None if feed_forward is None else \
+            build_part("norm", self.specs["feed_forward_norm"], dtype=dtype, device=device)
         self._native = _UNKNOWN
         self._native_generation = -1
 
     def named_parts(self) -> list[tuple[str, Part]]:
-        return [(self.specs["mixer_norm"].prefix, self.mixer_norm),
-                (self.specs["mixer"].prefix, self.mixer),
-                (self.specs["feed_forward_norm"].prefix, self.feed_forward_norm),
-                (self.specs["feed_forward"].prefix, self.feed_forward)]
+        parts = [(self.specs["mixer_norm"].prefix, self.mixer_norm), (self.specs["mixer"].prefix, self.mixer)]
+        if self.feed_forward is not None:
+            parts += [(self.specs["feed_forward_norm"].prefix, self.feed_forward_norm),
+                      (self.specs["feed_forward"].prefix, self.feed_forward)]
+        return parts
 
     def forward(self, stream: ResidualStream, ctx: LayerContext) -> None:
         if self._native is _UNKNOWN or self._native_generation != gemm.generation():
@@ -56,7 +61,8 @@ class PreNormBlock(Block):
             native_block.run_block(self._native, stream, ctx, window)
             return
         stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx))
-        stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm), ctx))
+        if self.feed_forward is not None:
+            stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm), ctx))
 
 
 register_part("block", "prenorm", PreNormBlock)

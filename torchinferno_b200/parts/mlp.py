@@ -46,3 +46,34 @@ class SwiGLUFeedForward(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+
+
+class DenseFeedForward(FeedForward):
+    """down(act(up(x))) without a gate: act = relu squared (``relu2``; the square in fp32).  No biases."""
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, activation: str = "relu2", up_name: str = "up",
+                 down_name: str = "down", dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        if activation != "relu2":
+            raise ValueError(f"unknown activation {activation!r}; known: ['relu2']")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.names = (up_name, down_name)
+        self.up_weight: LinearWeight | None = None
+        self.down_weight: LinearWeight | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        u, d = self.names
+        return [WeightSpec(u, (self.intermediate_size, self.hidden_size), std=self.hidden_size ** -0.5),
+                WeightSpec(d, (self.hidden_size, self.intermediate_size), std=self.intermediate_size ** -0.5)]
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        u, d = self.names
+        self.up_weight = LinearWeight(weights[u], few_rows_tcgen05=None)
+        self.down_weight = LinearWeight(weights[d], few_rows_tcgen05=None)
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        hidden = linear(x, self.up_weight)
+        return linear(ops.relu_squared(hidden, hidden), self.down_weight)
+
+
+register_part("feed_forward", "dense", DenseFeedForward)

@@ -64,8 +64,9 @@ class LayerNorm(Norm):
 
     def add_forward(self, delta, residual, out, rows=None):
         if rows is None:
-            ops.add_pair(residual, delta)
-            return ops.layernorm(residual, self.weight, self.bias, self.eps, out)
+            # (one launch: the sum into the 32-bit residual, then the norm of the new row)
+            ops.layernorm_tail(residual, self.eps, y=delta, y_norm=None, out=out, out_norm=(self.weight, self.bias))
+            return out
         # (with rows the delta is only looked at and stays pending)
         index = rows.long()
         picked = residual.index_select(0, index) + delta.index_select(0, index).to(torch.float32)

@@ -19,8 +19,36 @@ from torchinferno_b200.kernels import ops
 from torchinferno_b200.parts.base import LayerContext, PositionEncoding, register_part
 
 
+def yarn_frequencies(rot_dim: int, theta: float, factor: float, original: float, fast: float, slow: float) -> torch.Tensor:
+    """The YaRN law: pair i keeps its frequency f_i = theta^(-2i/rot) where it turns fast, gets f_i / factor where it
+    turns slowly, and a blend between.  With d(t) = rot * ln(original / (2 pi t)) / (2 ln theta), the pair index
+    that makes t turns over ``original`` positions, lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rot - 1)
+    and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is r_i f_i / factor + (1 - r_i) f_i.
+    Made in double precision, returned in fp32."""
+    i = torch.arange(rot_dim // 2, dtype=torch.float64)
+    freq = torch.tensor(float(theta), dtype=torch.float64) ** (-2.0 * i / rot_dim)
+
+    def pair_of(turns: float) -> float:
+        return rot_dim * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+
+    lo = max(math.floor(pair_of(fast)), 0)
+    hi = min(math.ceil(pair_of(slow)), rot_dim - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (freq / factor * ramp + freq * (1.0 - ramp)).to(torch.float32)
+
+
+def rotary_amplitude(scaling: Mapping[str, Any] | None) -> float:
+    """What cos and sin are multiplied by: 0.1 ln(factor) + 1 under the YaRN law, else 1."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 def rotary_frequencies(rot_dim: int, theta: float, scaling: Mapping[str, Any] | None = None) -> torch.Tensor:
     """The fp32 frequency table [rot_dim / 2], on the CPU."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return yarn_frequencies(rot_dim, float(theta), float(scaling["factor"]), float(scaling["original"]),
+                                float(scaling["fast"]), float(scaling["slow"]))
     exponent = torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim
     inv_freq = 1.0 / (theta ** exponent)
     if not scaling:
@@ -52,12 +80,17 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError("rot_dim must be even and at most head_dim")
         self.interleaved = bool(interleaved)
         self.inv_freq = rotary_frequencies(self.rot_dim, float(theta), scaling).to(device)
+        # cos and sin are multiplied by this (1 for every law but YaRN's); only kernels that take it as an argument
+        # may serve an encoding whose amplitude is not 1
+        self.amplitude = rotary_amplitude(scaling)
 
     def rotary_table(self):
         """(inv_freq, rot_dim, interleaved): what a kernel needs to apply this encoding itself."""
         return self.inv_freq, self.rot_dim, self.interleaved
 
     def encode_and_store(self, qkv, q_out, ctx: LayerContext, heads, kv_heads, head_dim):
+        if self.amplitude != 1.0:
+            raise ValueError("this rotary kernel takes no amplitude; a mixer that applies the table itself does")
         kv = ctx.kv
         write = kv is not None and kv.writes
         return ops.rope_append(
