@@ -456,7 +456,18 @@ def _design_configs(DESIGN_WIDTH: int, DESIGN_HEADS: int, kv_heads: int, dense_f
                           {"type": "attention", "mixer": dict(sigmoid, kv_from=0), "mlp": gated},
                           {"type": "mingru", "mixer": {"width": DESIGN_WIDTH}, "mlp": gated},
                           {"type": "attention", "mixer": sigmoid, "mlp": gated}]}
-    return {"zipedra": zipedra, "giforax": giforax, "llama": llama}
+    # Tibalorn beside the same Llama: the same head counts and head size over a window of 512 and blocks of 64, two
+    # state-space layers of twice the model's width in heads of 64 with a state of 128, the same dense feed-forward
+    windowed = {"heads": DESIGN_HEADS, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512, "pool": 64},
+                "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    ssd = {"heads": DESIGN_WIDTH // 32, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    tibalorn = {"architecture": "Tibalorn", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+                "logit_softcap": 30.0,
+                "layers": [{"type": "attention", "mixer": windowed, "mlp": dense},
+                           {"type": "mamba2", "mixer": ssd, "mlp": None},
+                           {"type": "mamba2", "mixer": ssd, "mlp": dense},
+                           {"type": "attention", "mixer": windowed, "mlp": dense}]}
+    return {"zipedra": zipedra, "giforax": giforax, "tibalorn": tibalorn, "llama": llama}
 
 
 def run_design(args) -> dict:
@@ -515,7 +526,9 @@ def run_design(args) -> dict:
         with contextlib.redirect_stdout(lines):
             own = {"zipedra": (["latent-attention"], ["linear-attention"], ["expert-product"]),
                    "giforax": (["sigmoid-attention"], ["sigmoid-attention", "--chunk", "2048"], ["gated-recurrence"], ["layer-tails"],
-                               ["expert-product"])}[args.design]
+                               ["expert-product"]),
+                   "tibalorn": (["pooled-window-attention"], ["state-space", "--heads", str(args.design_width // 32)],
+                                ["sigmoid-attention"], ["gated-recurrence"], ["layer-tails"])}[args.design]
             alone = () if args.design_no_kernels else (*own, ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
                                                        ["decode-attention", "--heads", "16", "--kv-heads", "8"])
             for argv in alone:
@@ -623,7 +636,7 @@ def main(argv=None) -> int:
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     parser.add_argument("--workloads", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS),
                         help="serving workloads of the smaller sizes to add to points")
-    parser.add_argument("--design", choices=["zipedra", "giforax"], default=None,
+    parser.add_argument("--design", choices=["zipedra", "giforax", "tibalorn"], default=None,
                         help="instead of the headline run: prefill and decode throughput of this design at layer sizes that "
                              "resemble a real model's, beside the closest Llama, and its kernels against the roofline")
     parser.add_argument("--design-width", type=int, default=DESIGN_WIDTH,

@@ -107,6 +107,23 @@ def pooled_window_weights(scores_tokens, scores_blocks, positions, size, pool, s
     return weights[..., :T], weights[..., T:]
 
 
+def windowed_pooled_attention(q, k, v, positions, size, pool, factor, sink):
+    """q [T, H, d] and k [T, G, d], v [T, G, dv] as a cache would hold them, of one sequence from its first token on.
+    Block b is the mean of the keys (values) of positions b * pool .. b * pool + pool - 1; query head h reads key head
+    h // (H / G); ``factor`` [H] multiplies the scores.  Returns the heads' sums [T, H, dv]."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    B = T // pool
+    k_blocks = k[:B * pool].reshape(B, pool, G, k.shape[2]).mean(dim=1)
+    v_blocks = v[:B * pool].reshape(B, pool, G, v.shape[2]).mean(dim=1)
+    rep = H // G
+    kh, vh = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    kbh, vbh = k_blocks.repeat_interleave(rep, dim=1), v_blocks.repeat_interleave(rep, dim=1)
+    s_tokens = torch.einsum("ihd,jhd->hij", q, kh) * factor[:, None, None]
+    s_blocks = torch.einsum("ihd,bhd->hib", q, kbh) * factor[:, None, None]
+    p_tokens, p_blocks = pooled_window_weights(s_tokens, s_blocks, positions, size, pool, sink)
+    return torch.einsum("hij,jhd->ihd", p_tokens, vh) + torch.einsum("hib,bhd->ihd", p_blocks, vbh)
+
+
 def attention_mixer(h, w, prefix, m, positions):
     """h: [T, W] normed input of one sequence whose positions are 0 .. T - 1."""
     T, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -119,18 +136,8 @@ def attention_mixer(h, w, prefix, m, positions):
     q, k = turn_halves(q, angle, rot["dims"], amplitude), turn_halves(k, angle, rot["dims"], amplitude)
     turn = value_angles(positions, dv, rot["base"])
     v = turn_halves(v, turn, dv)                             # a value is kept turned by its own position
-    size, pool = mask["size"], mask["pool"]
-    B = T // pool
-    k_blocks = k[:B * pool].view(B, pool, G, d).mean(dim=1)  # [B, G, d]
-    v_blocks = v[:B * pool].view(B, pool, G, dv).mean(dim=1)
-    rep = H // G
-    kh, vh = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
-    kbh, vbh = k_blocks.repeat_interleave(rep, dim=1), v_blocks.repeat_interleave(rep, dim=1)
-    factor = (float(m["scale"]) * w[prefix + "temp"])[:, None, None]
-    s_tokens = torch.einsum("ihd,jhd->hij", q, kh) * factor
-    s_blocks = torch.einsum("ihd,bhd->hib", q, kbh) * factor
-    p_tokens, p_blocks = pooled_window_weights(s_tokens, s_blocks, positions, size, pool, w[prefix + "sink"])
-    out = torch.einsum("hij,jhd->ihd", p_tokens, vh) + torch.einsum("hib,bhd->ihd", p_blocks, vbh)
+    out = windowed_pooled_attention(q, k, v, positions, mask["size"], mask["pool"], float(m["scale"]) * w[prefix + "temp"],
+                                    w[prefix + "sink"])
     out = turn_halves(out, -turn, dv)                        # and the sum is turned back by the query's
     gate = torch.sigmoid(h @ w[prefix + "g"].T)
     return (out.reshape(T, H * dv) * gate) @ w[prefix + "o"].T
@@ -148,29 +155,38 @@ def short_convolution(u, weight, bias):
 
 def group_rms(y, parts, eps):
     T, width = y.shape
-    y = y.view(T, parts, width // parts)
+    y = y.reshape(T, parts, width // parts)
     return (y / torch.sqrt(y.pow(2).mean(dim=-1, keepdim=True) + eps)).reshape(T, width)
 
 
+def state_space_scan(x, B, C, dt, a_log, d_skip, start=None):
+    """The recurrence alone, token by token.  x [T, H, P], B and C [T, G, N], dt [T, H] (already positive), per head
+    (its group g = head // (H / G)) a state S [N, P] that starts at zero (or at ``start`` [H, N, P]):
+    S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T;   y_t = S_t^T C_t + d_skip x_t.  Returns (y [T, H, P], S)."""
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    decay = torch.exp(-torch.exp(a_log) * dt)
+    S = torch.zeros((H, N, P), dtype=x.dtype) if start is None else start.clone()
+    y = torch.empty((T, H, P), dtype=x.dtype)
+    group = torch.arange(H) // (H // G)
+    for t in range(T):
+        S = decay[t][:, None, None] * S + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
+        y[t] = torch.einsum("hnp,hn->hp", S, C[t][group]) + d_skip[:, None] * x[t]
+    return y, S
+
+
 def mamba2_mixer(h, w, prefix, m, eps):
-    """The recurrence, token by token.  Per head (its group g = head // (heads / groups)), S [N, P]:
-    S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T;   y_t = S_t^T C_t + D x_t."""
+    """[z | x | B | C | dt] = W_in h; x, B, C pass the convolution and silu; dt = softplus(dt + dt_bias); the scan; the
+    heads side by side times silu(z), normed in ``norm_groups`` parts, times a weight, then W_o."""
     T, H, P, N, G = h.shape[0], m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * P
     proj = h @ w[prefix + "in"].T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     xbc = silu(short_convolution(xbc, w[prefix + "conv"], w[prefix + "conv.b"]))
-    x = xbc[:, :inner].view(T, H, P)
-    B = xbc[:, inner:inner + G * N].view(T, G, N)
-    C = xbc[:, inner + G * N:].view(T, G, N)
-    dt = softplus(dt + w[prefix + "dt_bias"])                 # [T, H]
-    decay = torch.exp(-torch.exp(w[prefix + "A_log"]) * dt)
-    S = torch.zeros((H, N, P), dtype=h.dtype)
-    y = torch.empty((T, H, P), dtype=h.dtype)
-    group = torch.arange(H) // (H // G)
-    for t in range(T):
-        S = decay[t][:, None, None] * S + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
-        y[t] = torch.einsum("hnp,hn->hp", S, C[t][group]) + w[prefix + "D"][:, None] * x[t]
+    x = xbc[:, :inner].reshape(T, H, P)
+    B = xbc[:, inner:inner + G * N].reshape(T, G, N)
+    C = xbc[:, inner + G * N:].reshape(T, G, N)
+    y, _ = state_space_scan(x, B, C, softplus(dt + w[prefix + "dt_bias"]), w[prefix + "A_log"], w[prefix + "D"])
     y = y.reshape(T, inner) * silu(z)
     return (group_rms(y, m["norm_groups"], eps) * w[prefix + "norm"]) @ w[prefix + "o"].T
 

@@ -11,6 +11,8 @@
     python -m torchinferno_b200.bench_kernels sigmoid-attention --tokens 2048 --batch 8 --context 2048 --chunk 512
     python -m torchinferno_b200.bench_kernels gated-recurrence --tokens 2048 --batch 8
     python -m torchinferno_b200.bench_kernels layer-tails --rows 2048
+    python -m torchinferno_b200.bench_kernels pooled-window-attention --tokens 2048 --batch 8 --context 2048 --window 512 --pool 64
+    python -m torchinferno_b200.bench_kernels state-space --tokens 2048 --batch 8
 
 Each run prints one JSON line per case: microseconds (median of CUDA-event timings, an L2 flush
 between iterations), the bytes or flops the kernel has to move or do, and the fraction of the
@@ -409,6 +411,89 @@ def run_layer_tails(args) -> None:
     report("add_rmsnorm", timer(lambda: ops.add_rmsnorm(delta, history[0], wt, 1e-6, out)), bytes_moved=rows * w * 12, rows=rows, hidden=w)
 
 
+def run_pooled_window_attention(args) -> None:
+    """The attention over a window plus pooled blocks on a prompt of --tokens (flops: both products over the tokens and
+    blocks a query sees) and on --batch single tokens at --context (bytes: the keys and values of the window and of the
+    blocks each query sees), with sink, temperature, rotated values and the output gate."""
+    h, k, d, v, page, window, pool = args.heads, args.kv_heads, args.head_dim, args.value_dim, args.page_size, args.window, args.pool
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+
+    def pages(n_entries, entries_per):
+        per = -(-entries_per // page)
+        pool_ = (torch.randn(n_entries * per, k * page * (d + v), device="cuda") * 0.5).to(torch.bfloat16)
+        table = torch.randperm(n_entries * per, device="cuda", dtype=torch.int32).view(n_entries, per).contiguous()
+        return pool_[:, :k * page * d].unflatten(1, (k, page, d)), pool_[:, k * page * d:].unflatten(1, (k, page, v)), table
+
+    seen = lambda p: min(p + 1, window) + max(0, p - window + 1) // pool
+    for mode in ("prompt", "single tokens"):
+        n_entries, ctx = (1, args.tokens) if mode == "prompt" else (args.batch, args.context)
+        keys, values, table = pages(n_entries, ctx)
+        bkeys, bvalues, btable = pages(n_entries, ctx // pool + 1)
+        n = ctx if mode == "prompt" else n_entries
+        q = torch.randn(n, h * d, device="cuda").to(torch.bfloat16)
+        gate = torch.randn(n, h * v, device="cuda").to(torch.bfloat16)
+        temp, sink = torch.ones(h, device="cuda"), torch.zeros(h, device="cuda")
+        vfreq = (10000.0 ** (-torch.arange(v // 2, dtype=torch.float64) * 2 / v)).float().cuda()
+        out = torch.empty(n, h * v, dtype=torch.bfloat16, device="cuda")
+        if mode == "prompt":
+            q_start, kv_start, slots, max_q = i32([0, n]), i32([0]), i32([0]), n
+            flops, moved = 2 * h * (d + v) * sum(seen(p) for p in range(ctx)), None
+        else:
+            q_start, kv_start, slots, max_q = i32(list(range(n + 1))), i32([ctx - 1] * n), i32(list(range(n))), 1
+            flops, moved = None, n * seen(ctx - 1) * k * (d + v) * 2
+        fn = lambda: ops.pooled_window_attention(q, out, q_start, kv_start, slots, keys, values, table, bkeys, bvalues, btable, n_entries,
+                                                 max_q, h, k, window=window, pool=pool, scale=0.09, temp=temp, sink=sink,
+                                                 value_freq=vfreq, gate=gate)
+        report(f"pooled_window_attention[{mode}]", timer(fn), flops=flops, bytes_moved=moved, entries=n_entries, context=ctx, heads=h,
+               kv_heads=k, head_dim=d, value_dim=v, window=window, pool=pool)
+    # the launch ahead of it: biases, the two rotations, the store into the pages; then the means of completed blocks
+    n = args.tokens
+    keys, values, table = pages(1, n)
+    bkeys, bvalues, btable = pages(1, n // pool + 1)
+    proj = torch.randn(n, (h + k) * d + k * v + h * v, device="cuda").to(torch.bfloat16)
+    q = torch.empty(n, h * d, dtype=torch.bfloat16, device="cuda")
+    freq = (10000.0 ** (-torch.arange(d // 4, dtype=torch.float64) * 4 / d)).float().cuda()
+    vfreq = (10000.0 ** (-torch.arange(v // 2, dtype=torch.float64) * 2 / v)).float().cuda()
+    positions, token_slot = i32(list(range(n))), i32([0] * n)
+    bias = [torch.zeros(w, device="cuda") for w in (h * d, k * d, k * v)]
+    fn = lambda: ops.rotary_kv_append(proj, 0, h * d, (h + k) * d, q, keys, values, positions, token_slot, table, freq, vfreq, h, k, d, v,
+                                      rot_dim=d // 2, amplitude=1.07, q_bias=bias[0], k_bias=bias[1], v_bias=bias[2])
+    report("rotary_kv_append[prompt]", timer(fn), bytes_moved=n * ((h + k) * d + k * v) * 4, tokens=n)
+    fn = lambda: ops.pool_blocks(keys, values, table, bkeys, bvalues, btable, positions, token_slot, pool)
+    report("pool_blocks[prompt]", timer(fn), bytes_moved=n * k * (d + v) * 2 + (n // pool) * k * (d + v) * 2, tokens=n, pool=pool)
+
+
+def run_state_space(args) -> None:
+    """The state-space mixer's kernels on a prompt of --tokens and on --batch single tokens: the short convolution, the
+    scan (bytes: the rows [x | B | C] and the step sizes read, the 32-bit sums written, the state read and written) and
+    the gate with the norm in parts."""
+    heads, p_, n_state, groups, taps = args.heads, args.head_dim, args.state, args.groups, args.taps
+    inner, channels = heads * p_, heads * p_ + 2 * groups * n_state
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+    for mode in ("prompt", "single tokens"):
+        n_entries, n = (1, args.tokens) if mode == "prompt" else (args.batch, args.batch)
+        proj = (torch.randn(n, 2 * inner + 2 * groups * n_state + heads, device="cuda") * 0.5).to(torch.bfloat16)
+        xbc = torch.empty(n, channels, dtype=torch.bfloat16, device="cuda")
+        state = torch.zeros(n_entries, heads * n_state * p_ + (taps - 1) * channels, device="cuda")
+        q_start = i32([0, n]) if mode == "prompt" else i32(list(range(n + 1)))
+        slots, max_q = i32(list(range(n_entries))), (n if mode == "prompt" else 1)
+        cw, cb = torch.randn(channels, taps, device="cuda") * 0.5, torch.zeros(channels, device="cuda")
+        vec = [torch.zeros(heads, device="cuda") for _ in range(3)]
+        y = torch.empty(n, inner, device="cuda")
+        rows = torch.empty(n, inner, dtype=torch.bfloat16, device="cuda")
+        weight = torch.ones(inner, device="cuda")
+        fn = lambda: ops.short_conv(proj, inner, cw, cb, state, heads * n_state * p_, q_start, slots, xbc, n_entries, max_q, silu=True)
+        report(f"short_conv[{mode}]", timer(fn), bytes_moved=n * channels * 4 + n_entries * (taps - 1) * channels * 8, tokens=n, channels=channels)
+        fn = lambda: ops.ssd_scan(xbc, proj, inner + channels, vec[0], vec[1], vec[2], state, q_start, slots, y, n_entries, heads=heads,
+                                  groups=groups, state_dim=n_state, head_dim=p_)
+        report(f"ssd_scan[{mode}]", timer(fn), bytes_moved=n * (channels * 2 + heads * 2 + inner * 4) + n_entries * heads * n_state * p_ * 8,
+               flops=None, tokens=n, heads=heads, head_dim=p_, state=n_state, scan_gflop=round(n * heads * p_ * n_state * 6 / 1e9, 2))
+        fn = lambda: ops.gated_group_norm(y, proj, 0, weight, 1e-6, rows, args.norm_groups)
+        report(f"gated_group_norm[{mode}]", timer(fn), bytes_moved=n * inner * 8, tokens=n, width=inner)
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m torchinferno_b200.bench_kernels", description=__doc__.splitlines()[0])
     parser.add_argument("--ordinary-launches", action="store_true",
@@ -509,6 +594,30 @@ def main(argv=None) -> int:
     p.add_argument("--depth", type=int, default=5)
     p.add_argument("--iters", type=int, default=10)
     p.set_defaults(func=run_layer_tails)
+    p = sub.add_parser("pooled-window-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=128)
+    p.add_argument("--window", type=int, default=512)
+    p.add_argument("--pool", type=int, default=64)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_pooled_window_attention)
+    p = sub.add_parser("state-space")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--heads", type=int, default=64)
+    p.add_argument("--head-dim", type=int, default=64)
+    p.add_argument("--state", type=int, default=128)
+    p.add_argument("--groups", type=int, default=1)
+    p.add_argument("--taps", type=int, default=4)
+    p.add_argument("--norm-groups", type=int, default=1)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_state_space)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")

@@ -12,11 +12,13 @@
 //                      exp(sink[h]) added to its denominator; the head's sum of values is turned back by -i over the
 //                      value pairs and multiplied element by element by sigmoid(gate)
 //
-// Scores, the softmax, the sums over values, the turning back and the gate are fp32.  One warp owns one (query token,
-// query head) row from start to end and walks first the blocks, then the tokens, 32 at a time, aligned to absolute
-// block numbers / positions, in rising order: a row's arithmetic depends only on its own position, never on how the
-// batch was cut, which rows share the thread block, or which pages hold the keys.
-#include "common.cuh"
+// Scores, the softmax, the sums over values, the turning back and the gate are fp32.  Two kernels.  On the CUDA cores
+// (32-bit, single tokens, any head size) one warp owns one (query token, query head) row from start to end and walks
+// first the blocks, then the tokens, 32 at a time, aligned to absolute block numbers / positions, in rising order: a
+// row's arithmetic depends only on its own position, never on how the batch was cut, which rows share the thread
+// block, or which pages hold the keys.  On the tensor cores (bf16 steps that hold a portion of a prompt) the same
+// walk runs in tiles of 64 with mma.sync, see below.
+#include "mma.cuh"
 #include <math_constants.h>
 
 namespace tib {
@@ -364,6 +366,331 @@ static int pwa_launch(const void* q, void* out, const PwaArgs& a, int n_entries,
   return TIB_OK;
 }
 
+// ------------------------------------------------------------ tensor cores
+// 64 rows (tokens x the query heads of one kv head) against tiles of 64 keys, four warps of 16 rows: first the tiles of
+// block means (aligned to absolute block numbers), then the tiles of tokens (aligned to absolute positions), both in
+// rising order, so a row's sums do not depend on how the prompt was cut or on what else the step holds.  Keys and values
+// of a tile come in by cp.async, row by row from their pages, two stages; rows the tile's queries cannot see are
+// zero-filled (unwritten cache may hold anything) and masked.  Scores accumulate in fp32; the softmax runs in fp32 on
+// scores in units of ln 2; the weights enter the second product as a high bf16 part plus the remainder, so that they
+// keep 16 bits.  The rows' sums then pass through shared memory, where pairs (m, m + vdim / 2) meet for the turning back.
+constexpr int kPmRows = 64, kPmKeys = 64, kPmThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(kPmThreads)
+pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, PwaArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int KP = DK + 8, VP = DV + 8;        // padded rows: ldmatrix rows fall in different banks
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);          // [64][KP]
+  __nv_bfloat16* k_s = q_s + kPmRows * KP;                                 // [2][64][KP]
+  __nv_bfloat16* v_s = k_s + 2 * kPmKeys * KP;                             // [2][64][VP]
+  __shared__ long long page_base[2][kPmKeys];
+  __shared__ int key_row[2][kPmKeys];
+
+  const int d = a.dim, vd = a.vdim;
+  const int entry = blockIdx.y;
+  const int group = a.heads / a.kv_heads;
+  const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
+  const int kvh = blockIdx.z / chunks;
+  const int g0 = (blockIdx.z - kvh * chunks) * a.group_chunk;
+  const int gc = min(a.group_chunk, group - g0);
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int t0 = blockIdx.x * a.q_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(a.q_tile, q_len - t0);
+  const int nrows = nt * gc;
+  const int pos0 = a.kv_start[entry] + t0;
+  const int last_pos = pos0 + nt - 1;
+  const int slot = a.slots[entry];
+  const int* ttable = a.tokens.block_table + (size_t)slot * a.tokens.table_stride;
+  const int* btable = a.pool > 0 ? a.blocks.block_table + (size_t)slot * a.blocks.table_stride : nullptr;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // how many blocks the last query of the tile sees, and the first token any query of the tile sees
+  const int n_blocks = a.pool > 0 ? max(0, last_pos - a.window + 1) / a.pool : 0;
+  const int first_key = max(0, pos0 - a.window + 1);
+  const int steps_b = (n_blocks + kPmKeys - 1) / kPmKeys;
+  const int s_lo = first_key / kPmKeys, s_hi = last_pos / kPmKeys;
+  const int steps = steps_b + (s_hi - s_lo + 1);
+
+  auto fetch = [&](int stage, int step) {
+    const bool pooled = step < steps_b;
+    const PwaCache& c = pooled ? a.blocks : a.tokens;
+    // where every key of the tile lives, once: its page's first element and its row in the page
+    if (tid < kPmKeys) {
+      const int idx = (pooled ? step : s_lo + step - steps_b) * kPmKeys + tid;
+      long long base = -1;
+      int row = 0;
+      if (pooled ? idx < n_blocks : (idx <= last_pos && idx >= first_key)) {
+        const int page = pwa_page(c, pooled ? btable : ttable, idx, a.error_word, 0x10000 + entry);
+        if (page >= 0) {
+          base = (long long)page * c.page_stride;
+          row = kvh * c.page_size + idx % c.page_size;
+        }
+      }
+      page_base[stage][tid] = base;
+      key_row[stage][tid] = row;
+    }
+    __syncthreads();
+    const __nv_bfloat16* k_pages = reinterpret_cast<const __nv_bfloat16*>(c.keys);
+    const __nv_bfloat16* v_pages = reinterpret_cast<const __nv_bfloat16*>(c.values);
+    constexpr int KPIECES = DK / 8, VPIECES = DV / 8;
+    for (int e = tid; e < kPmKeys * KPIECES; e += kPmThreads) {
+      const int j = e / KPIECES, cc = (e - j * KPIECES) * 8;
+      const long long base = page_base[stage][j];
+      const bool ok = base >= 0 && cc < d;
+      cp_async16(k_s + ((size_t)stage * kPmKeys + j) * KP + cc, k_pages + (ok ? base + (long long)key_row[stage][j] * d + cc : 0), ok);
+    }
+    for (int e = tid; e < kPmKeys * VPIECES; e += kPmThreads) {
+      const int j = e / VPIECES, cc = (e - j * VPIECES) * 8;
+      const long long base = page_base[stage][j];
+      const bool ok = base >= 0 && cc < vd;
+      cp_async16(v_s + ((size_t)stage * kPmKeys + j) * VP + cc, v_pages + (ok ? base + (long long)key_row[stage][j] * vd + cc : 0), ok);
+    }
+    cp_async_commit();
+  };
+
+  // queries: 16-byte pieces, rows past the tile's end and padding columns are zero
+  {
+    constexpr int QPIECES = DK / 8;
+    for (int e = tid; e < kPmRows * QPIECES; e += kPmThreads) {
+      const int r = e / QPIECES, cc = (e - r * QPIECES) * 8;
+      const bool ok = r < nrows && cc < d;
+      const int t = ok ? r / gc : 0, g = ok ? r - t * gc : 0;
+      const __nv_bfloat16* src = q + (size_t)(row0 + t0 + t) * a.heads * d + (size_t)(kvh * group + g0 + g) * d + (ok ? cc : 0);
+      cp_async16(q_s + (size_t)r * KP + cc, src, ok);
+    }
+  }
+  fetch(0, 0);            // (there is always the tile of the query's own position)
+
+  // this thread's two rows: g8 and g8 + 8 of the warp's sixteen
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int row_base = warp * 16;
+  int qpos[2], lo[2], seen[2];
+  float factor[2], m[2], l[2];
+  bool live[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = row_base + g8 + 8 * h;
+    live[h] = r < nrows;
+    const int t = live[h] ? r / gc : 0, g = live[h] ? r - t * gc : 0;
+    qpos[h] = pos0 + t;
+    lo[h] = max(0, qpos[h] - a.window + 1);
+    seen[h] = a.pool > 0 ? lo[h] / a.pool : 0;       // blocks 0 .. seen - 1 lie wholly behind the window
+    factor[h] = a.scale * (a.temp ? a.temp[kvh * group + g0 + g] : 1.f) * kLog2e;
+    m[h] = -CUDART_INF_F;
+    l[h] = 0.f;
+  }
+  constexpr int NT = kPmKeys / 8;
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+  // what the warp's rows see, for skipping whole tiles
+  const int warp_first = pos0 + row_base / gc, warp_last = pos0 + min(nrows - 1, row_base + 15) / gc;
+  const int warp_lo = max(0, warp_first - a.window + 1);
+  const int warp_seen = a.pool > 0 ? max(0, warp_last - a.window + 1) / a.pool : 0;
+
+  for (int step = 0; step < steps; ++step) {
+    const int stage = step & 1;
+    if (step + 1 < steps) {
+      fetch(stage ^ 1, step + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bool pooled = step < steps_b;
+    const int base = (pooled ? step : s_lo + step - steps_b) * kPmKeys;
+    // (a warp whose rows see nothing of this tile still passes the barriers)
+    const bool any = row_base < nrows && (pooled ? base < warp_seen : (base <= warp_last && base + kPmKeys - 1 >= warp_lo));
+    if (any) {
+      const __nv_bfloat16* kt = k_s + (size_t)stage * kPmKeys * KP;
+      const __nv_bfloat16* vt = v_s + (size_t)stage * kPmKeys * VP;
+      float s[NT][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DK; kk += 16) {
+        uint32_t af[4];
+        ldmatrix_x4(af, q_s + (size_t)(row_base + (lane & 15)) * KP + kk + (lane >> 4) * 8);
+#pragma unroll
+        for (int j = 0; j < NT / 2; ++j) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, kt + (size_t)(j * 16 + ((lane >> 4) << 3) + (lane & 7)) * KP + kk + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * j], af, bf[0], bf[1]);
+          mma_bf16(s[2 * j + 1], af, bf[2], bf[3]);
+        }
+      }
+      // mask, then the streaming softmax in fp32 (scores in units of ln 2)
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int idx = base + n * 8 + 2 * t4 + (c & 1);
+          const bool allowed = live[h] && (pooled ? idx < seen[h] : (idx <= qpos[h] && idx >= lo[h]));
+          s[n][c] = allowed ? s[n][c] * factor[h] : -CUDART_INF_F;
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[h], mx);
+        const float top = m_new == -CUDART_INF_F ? 0.f : m_new;
+        const float alpha = exp2f(m[h] - top);
+        m[h] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          s[n][2 * h] = exp2f(s[n][2 * h] - top);
+          s[n][2 * h + 1] = exp2f(s[n][2 * h + 1] - top);
+          sum += s[n][2 * h] + s[n][2 * h + 1];
+        }
+        l[h] = l[h] * alpha + sum;
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int n = 0; n < DV / 8; ++n) {
+            o[n][2 * h] *= alpha;
+            o[n][2 * h + 1] *= alpha;
+          }
+        }
+      }
+      uint32_t p_hi[NT / 2][4], p_lo[NT / 2][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int kk = n >> 1, half = (n & 1) * 2;
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(s[n][0], s[n][1]), h23 = __floats2bfloat162_rn(s[n][2], s[n][3]);
+        p_hi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+        p_hi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+        const float2 f01 = bf16x2_floats(h01), f23 = bf16x2_floats(h23);
+        p_lo[kk][half] = pack_bf16(s[n][0] - f01.x, s[n][1] - f01.y);
+        p_lo[kk][half + 1] = pack_bf16(s[n][2] - f23.x, s[n][3] - f23.y);
+      }
+#pragma unroll
+      for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t bv[DV / 16][4];
+#pragma unroll
+        for (int dn = 0; dn < DV / 16; ++dn) {
+          ldmatrix_x4_trans(bv[dn], vt + (size_t)(kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
+          mma_bf16(o[2 * dn], p_hi[kk], bv[dn][0], bv[dn][1]);
+          mma_bf16(o[2 * dn + 1], p_hi[kk], bv[dn][2], bv[dn][3]);
+        }
+#pragma unroll
+        for (int dn = 0; dn < DV / 16; ++dn) {
+          mma_bf16(o[2 * dn], p_lo[kk], bv[dn][0], bv[dn][1]);
+          mma_bf16(o[2 * dn + 1], p_lo[kk], bv[dn][2], bv[dn][3]);
+        }
+      }
+    }
+    __syncthreads();      // the stage is free for the fetch after next
+  }
+
+  // the rows' sums, divided by the softmax's denominator (with the number that has no key), into shared memory
+  float* o_s = reinterpret_cast<float*>(k_s);           // [64][DV] floats over the key and value stages, which adjoin
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = l[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    float inv = 0.f;
+    if (live[h]) {
+      const int r = row_base + g8 + 8 * h;
+      float top = m[h], denom = sum;
+      if (a.sink) {
+        const float sink = a.sink[kvh * group + g0 + (r - (r / gc) * gc)] * kLog2e;
+        top = fmaxf(m[h], sink);
+        denom = sum * exp2f(m[h] - top) + exp2f(sink - top);
+      }
+      inv = exp2f(m[h] - top) / denom;
+    }
+    const int r = row_base + g8 + 8 * h;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      o_s[(size_t)r * DV + n * 8 + 2 * t4] = o[n][2 * h] * inv;
+      o_s[(size_t)r * DV + n * 8 + 2 * t4 + 1] = o[n][2 * h + 1] * inv;
+    }
+  }
+  __syncthreads();
+  const int o_width = a.heads * vd;
+  const int half = vd / 2;
+  const int per_row = a.vfreq ? half : vd;
+  const __nv_bfloat16* gate = reinterpret_cast<const __nv_bfloat16*>(a.gate);
+  for (int e = tid; e < nrows * per_row; e += kPmThreads) {
+    const int r = e / per_row, mm = e - r * per_row;
+    const int t = r / gc, g = r - t * gc;
+    const int head = kvh * group + g0 + g;
+    const size_t token = (size_t)(row0 + t0 + t);
+    __nv_bfloat16* dst = out + token * o_width + (size_t)head * vd;
+    const float* o_row = o_s + (size_t)r * DV;
+    if (a.vfreq) {
+      // turn the pair (mm, mm + half) back by the query's position: (u, v) -> (u cos + v sin, v cos - u sin)
+      const float angle = (float)(pos0 + t) * a.vfreq[mm];
+      const float c = cosf(angle), sn = sinf(angle);
+      float u = rope_lo(o_row[mm], o_row[mm + half], c, -sn), v = rope_hi(o_row[mm], o_row[mm + half], c, -sn);
+      if (gate) {
+        const float gu = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * vd + mm]
+                                                 : __bfloat162float(gate[token * a.ld_gate + head * vd + mm]);
+        const float gv = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * vd + mm + half]
+                                                 : __bfloat162float(gate[token * a.ld_gate + head * vd + mm + half]);
+        u *= 1.f / (1.f + expf(-gu));
+        v *= 1.f / (1.f + expf(-gv));
+      }
+      dst[mm] = __float2bfloat16_rn(u);
+      dst[mm + half] = __float2bfloat16_rn(v);
+    } else {
+      float u = o_row[mm];
+      if (gate) {
+        const float gu = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[token * a.ld_gate + head * vd + mm]
+                                                 : __bfloat162float(gate[token * a.ld_gate + head * vd + mm]);
+        u *= 1.f / (1.f + expf(-gu));
+      }
+      dst[mm] = __float2bfloat16_rn(u);
+    }
+  }
+}
+
+template <int DK, int DV>
+static int pwa_launch_mma(const void* q, void* out, PwaArgs a, int n_entries, int max_q_len, cudaStream_t stream) {
+  static_assert(kPmRows * DV * sizeof(float) <= 2 * kPmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the rows' sums fit the stages");
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kPmRows * (DK + 8) + 2 * (size_t)kPmKeys * (DK + 8) + 2 * (size_t)kPmKeys * (DV + 8));
+  auto kern = pwa_attention_mma_kernel<DK, DV>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int group = a.heads / a.kv_heads;
+  a.group_chunk = group < kPmRows ? group : kPmRows;
+  a.q_tile = kPmRows / a.group_chunk;
+  const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
+  if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
+  const dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, a.kv_heads * chunks);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kPmThreads, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, a);
+  return TIB_OK;
+}
+
+// Whether the tensor-core kernel takes these shapes (bf16; rows of 16-byte pieces in every array it copies from).
+static bool pwa_mma_takes(const PwaArgs& a, const void* q) {
+  const bool pieces = a.dim % 8 == 0 && a.vdim % 8 == 0 && a.dim <= 128 && a.vdim <= 128;
+  uintptr_t bits = (uintptr_t)q | (uintptr_t)a.tokens.keys | (uintptr_t)a.tokens.values;
+  bool strides = a.tokens.page_stride % 8 == 0;
+  if (a.pool > 0) {
+    bits |= (uintptr_t)a.blocks.keys | (uintptr_t)a.blocks.values;
+    strides = strides && a.blocks.page_stride % 8 == 0;
+  }
+  return pieces && strides && (bits & 15) == 0;
+}
+
 static PwaCache pwa_cache(void* keys, void* values, const int* table, int table_stride, int page_size, int64_t page_stride, int num_pages) {
   PwaCache c;
   c.keys = keys; c.values = values; c.block_table = table; c.table_stride = table_stride; c.page_size = page_size;
@@ -429,6 +756,7 @@ TIB_API int tib_pool_blocks(const void* k_pages, const void* v_pages, const int*
 
 // q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, heads * vdim] logits (row stride ld_gate, its
 // own dtype) or null; temp, sink: [heads] fp32 or null; vfreq: [vdim / 2] fp32 or null.  pool 0: the window alone.
+// force_simt: the CUDA-core kernel also where the tensor-core kernel would take the step.
 TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_start, const int* kv_start, const int* slots,
                                         const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                                         int page_size, int64_t page_stride, int num_pages, const void* bk_pages,
@@ -436,7 +764,7 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
                                         int64_t b_page_stride, int b_num_pages, int n_entries, int max_q_len, int heads,
                                         int kv_heads, int dim, int vdim, int window, int pool, float scale, const float* temp,
                                         const float* sink, const float* vfreq, const void* gate, int gate_dtype, int64_t ld_gate,
-                                        int* error_word, int dtype, cudaStream_t stream) {
+                                        int* error_word, int dtype, int force_simt, cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!q || !out || !q_start || !kv_start || !slots || !k_pages || !v_pages || !block_table) return TIB_E_ARG;
   if (pool > 0 && (!bk_pages || !bv_pages || !b_table || b_page_size < 1)) return TIB_E_ARG;
@@ -455,6 +783,14 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
   a.q_tile = kPwaRows / a.group_chunk;
   const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
   if ((int64_t)kv_heads * chunks > 65535) return TIB_E_SIZE;
+  // A step with a portion of a prompt in it runs on the tensor cores (bf16); single tokens, 32-bit, and head sizes
+  // that are no multiples of 8 run on the CUDA cores.
+  if (dtype == TIB_BF16 && !force_simt && (int64_t)max_q_len * a.group_chunk > 16 && pwa_mma_takes(a, q)) {
+    if (dim <= 64 && vdim <= 64) return pwa_launch_mma<64, 64>(q, out, a, n_entries, max_q_len, stream);
+    if (dim <= 64) return pwa_launch_mma<64, 128>(q, out, a, n_entries, max_q_len, stream);
+    if (vdim <= 64) return pwa_launch_mma<128, 64>(q, out, a, n_entries, max_q_len, stream);
+    return pwa_launch_mma<128, 128>(q, out, a, n_entries, max_q_len, stream);
+  }
   const int dpl = (vdim + 31) / 32;
 #define TIB_PWA_DISPATCH(T)                                                              \
   (dpl <= 1 ? pwa_launch<T, 1>(q, out, a, n_entries, max_q_len, stream)                  \

@@ -1323,11 +1323,13 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
                             max_q_len: int, heads: int, kv_heads: int, *, window: int, pool: int, scale: float,
                             temp: torch.Tensor | None = None, sink: torch.Tensor | None = None,
                             value_freq: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                            error_word: torch.Tensor | None = None) -> torch.Tensor:
+                            error_word: torch.Tensor | None = None, force_simt: bool = False) -> torch.Tensor:
     """Per head, out[i] = sigmoid(gate[i]) * turn_back_i(sum_j w_ij v_j + sum_b w_ib V_b): softmax weights over the tokens j
     with 0 <= i - j < window and the blocks b of ``pool`` positions with b * pool + pool - 1 <= i - window (their means K_b,
     V_b from the strided pages), scores q . k * scale * temp[h], exp(sink[h]) added to the denominator; turn_back undoes at
-    position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone."""
+    position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone.
+    bfloat16 steps that hold a portion of a prompt run on the tensor cores when the head sizes are multiples of 8 up to
+    128, unless ``force_simt``."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim = keys.shape[3], values.shape[3]
     n = q.shape[0]
@@ -1356,5 +1358,5 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
         _ptr(block_block_table if pool > 0 else None), c_int(b_table_stride), c_int(b_page_size), c_int64(b_stride), c_int(b_pages),
         c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(window), c_int(pool),
         c_float(scale), _ptr(temp), _ptr(sink), _ptr(value_freq), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
-        c_int64(ld_gate), _ptr(error_word), c_int(_code(q.dtype)), _stream()))
+        c_int64(ld_gate), _ptr(error_word), c_int(_code(q.dtype)), c_int(int(force_simt)), _stream()))
     return out

@@ -40,6 +40,8 @@ def yarn_frequencies(rot_dim: int, theta: float, factor: float, original: float,
 def rotary_amplitude(scaling: Mapping[str, Any] | None) -> float:
     """What cos and sin are multiplied by: 0.1 ln(factor) + 1 under the YaRN law, else 1."""
     if scaling and scaling.get("rope_type") == "yarn":
+        if "factor" not in scaling:
+            raise ValueError("the yarn law lacks ['factor']")
         return 0.1 * math.log(float(scaling["factor"])) + 1.0
     return 1.0
 
@@ -47,6 +49,9 @@ def rotary_amplitude(scaling: Mapping[str, Any] | None) -> float:
 def rotary_frequencies(rot_dim: int, theta: float, scaling: Mapping[str, Any] | None = None) -> torch.Tensor:
     """The fp32 frequency table [rot_dim / 2], on the CPU."""
     if scaling and scaling.get("rope_type") == "yarn":
+        missing = [key for key in ("factor", "original", "fast", "slow") if key not in scaling]
+        if missing:
+            raise ValueError(f"the yarn law lacks {missing}")
         return yarn_frequencies(rot_dim, float(theta), float(scaling["factor"]), float(scaling["original"]),
                                 float(scaling["fast"]), float(scaling["slow"]))
     exponent = torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim
