@@ -388,8 +388,8 @@ def test_a_sink_takes_weight_and_gives_nothing():
                                                                 (6, 5, 7, 3, 1, 2), (8, 64, 128, 1, 4, 1)])
 def test_state_space_mixer_alone_in_portions_over_its_state(dtype, heads, vdim, state, groups, conv, parts):
     """Portions that end just before, at and just after the kernels' runs of 16 and 64 tokens, portions shorter than the
-    convolution's reach (its carried inputs then move along by less than their number), long ones, single tokens; two
-    requests in one step; a slot used again starts from zero."""
+    convolution's reach (its carried inputs then move along by less than their number), long ones (which the scan cuts
+    into runs) beside single tokens and beside other long ones, single tokens; a slot used again starts from zero."""
     need_gpu()
     from torchinferno_b200.cache.manager import CacheManager
     from torchinferno_b200.parts.base import LayerContext, PartSpec, build_part
@@ -400,7 +400,7 @@ def test_state_space_mixer_alone_in_portions_over_its_state(dtype, heads, vdim, 
         "eps": eps}), dtype=dtype, device=CUDA)
     w = _random_weights(mixer, 4, dtype, "mix.")
     g = torch.Generator().manual_seed(state)
-    plan = ((63, 0), (1, 7), (2, 0), (1, 1), (1, 2), (64, 1), (65, 0), (1, 64), (15, 3), (17, 0), (200, 0), (1, 0), (1, 8), (130, 0))
+    plan = ((63, 0), (1, 7), (2, 0), (1, 1), (1, 2), (64, 1), (65, 0), (1, 64), (15, 3), (17, 0), (200, 2), (1, 0), (1, 8), (130, 70))
     T = sum(n for n, _ in plan)
     x = torch.randn(T, W, generator=g).to(torch.bfloat16).to(dtype)
     other = torch.randn(sum(k for _, k in plan), W, generator=g).to(torch.bfloat16).to(dtype)
@@ -429,10 +429,12 @@ def test_state_space_mixer_alone_in_portions_over_its_state(dtype, heads, vdim, 
     assert (out.cpu().double() - want_other[:5]).abs().max() <= tol * want_other.abs().max()
 
 
-def test_the_scan_keeps_a_first_token_through_a_long_quiet_run_and_forgets_at_the_rate_it_is_given():
+@pytest.mark.parametrize("cut", [False, True])
+def test_the_scan_keeps_a_first_token_through_a_long_quiet_run_and_forgets_at_the_rate_it_is_given(cut):
     """Step sizes made by hand: the first token writes the state, the 500 that follow have steps of about 1e-9 (they
     neither write nor let it decay), in portions and single tokens.  A state that is reset, scaled or lost at a run's or
-    a portion's edge shows in the last outputs.  A second head decays by a known factor per token."""
+    a portion's edge shows in the last outputs.  A second head decays by a known factor per token.  ``cut``: the kernel
+    is told the portions' lengths, so it cuts the long ones into runs that it walks side by side."""
     need_gpu()
     from torchinferno_b200.kernels import ops
     H, P, N, T = 2, 12, 10, 501
@@ -454,7 +456,8 @@ def test_the_scan_keeps_a_first_token_through_a_long_quiet_run_and_forgets_at_th
     for n in (1, 15, 16, 17, 63, 64, 129, 1, 1, 194):
         q_start = torch.tensor([0, n], dtype=torch.int32, device=CUDA)
         ops.ssd_scan(xbc[at:at + n], raw[at:at + n].cuda().contiguous(), 0, dt_bias.cuda(), a_log.cuda(), d_skip.cuda(), state, q_start,
-                     torch.tensor([1], dtype=torch.int32, device=CUDA), y[at:at + n], 1, heads=H, groups=1, state_dim=N, head_dim=P)
+                     torch.tensor([1], dtype=torch.int32, device=CUDA), y[at:at + n], 1, heads=H, groups=1, state_dim=N, head_dim=P,
+                     max_q_len=n if cut else None)
         at += n
     assert at == T and (y.cpu().double() - want.reshape(T, H * P)).abs().max() <= 1e-5 * want.abs().max()
     assert (state[1, :H * N * P].cpu().double() - S.reshape(-1)).abs().max() <= 1e-5 * S.abs().max()

@@ -487,7 +487,7 @@ def run_state_space(args) -> None:
         fn = lambda: ops.short_conv(proj, inner, cw, cb, state, heads * n_state * p_, q_start, slots, xbc, n_entries, max_q, silu=True)
         report(f"short_conv[{mode}]", timer(fn), bytes_moved=n * channels * 4 + n_entries * (taps - 1) * channels * 8, tokens=n, channels=channels)
         fn = lambda: ops.ssd_scan(xbc, proj, inner + channels, vec[0], vec[1], vec[2], state, q_start, slots, y, n_entries, heads=heads,
-                                  groups=groups, state_dim=n_state, head_dim=p_)
+                                  groups=groups, state_dim=n_state, head_dim=p_, max_q_len=max_q)
         report(f"ssd_scan[{mode}]", timer(fn), bytes_moved=n * (channels * 2 + heads * 2 + inner * 4) + n_entries * heads * n_state * p_ * 8,
                flops=None, tokens=n, heads=heads, head_dim=p_, state=n_state, scan_gflop=round(n * heads * p_ * n_state * 6 / 1e9, 2))
         fn = lambda: ops.gated_group_norm(y, proj, 0, weight, 1e-6, rows, args.norm_groups)

@@ -13,10 +13,10 @@
 //                      value pairs and multiplied element by element by sigmoid(gate)
 //
 // Scores, the softmax, the sums over values, the turning back and the gate are fp32.  Two kernels.  On the CUDA cores
-// (32-bit, single tokens, any head size) one warp owns one (query token, query head) row from start to end and walks
+// (32-bit, any head size) one warp owns one (query token, query head) row from start to end and walks
 // first the blocks, then the tokens, 32 at a time, aligned to absolute block numbers / positions, in rising order: a
 // row's arithmetic depends only on its own position, never on how the batch was cut, which rows share the thread
-// block, or which pages hold the keys.  On the tensor cores (bf16 steps that hold a portion of a prompt) the same
+// block, or which pages hold the keys.  On the tensor cores (bf16, head sizes that are multiples of 8) the same
 // walk runs in tiles of 64 with mma.sync, see below.
 #include "mma.cuh"
 #include <math_constants.h>
@@ -144,10 +144,18 @@ __global__ void __launch_bounds__(128) pwa_pool_kernel(PwaPoolArgs a) {
     const int dd = is_k ? e : e - a.dim, w = is_k ? a.dim : a.vdim;
     const T* base = reinterpret_cast<const T*>(is_k ? a.tokens.keys : a.tokens.values);
     float sum = 0.f;
-    for (int j = 0; j < a.pool; ++j) {
-      const int page = pwa_page(a.tokens, ttable, first + j, a.error_word, 0x50000 + (t & 0xffff));
-      if (page < 0) continue;
-      sum += to_f32(base[(size_t)page * a.tokens.page_stride + ((size_t)kvh * a.tokens.page_size + (first + j) % a.tokens.page_size) * w + dd]);
+    constexpr int AHEAD = 8;              // loads in flight; the sum still runs in rising order of position
+    for (int j0 = 0; j0 < a.pool; j0 += AHEAD) {
+      float part[AHEAD];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const int j = j0 + u;
+        const int page = j < a.pool ? pwa_page(a.tokens, ttable, first + j, a.error_word, 0x50000 + (t & 0xffff)) : -1;
+        part[u] = page < 0 ? 0.f
+                           : to_f32(base[(size_t)page * a.tokens.page_stride + ((size_t)kvh * a.tokens.page_size + (first + j) % a.tokens.page_size) * w + dd]);
+      }
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) sum += part[u];
     }
     T* out = reinterpret_cast<T*>(is_k ? a.blocks.keys : a.blocks.values);
     out[(size_t)bpage * a.blocks.page_stride + ((size_t)kvh * a.blocks.page_size + b % a.blocks.page_size) * w + dd] = from_f32<T>(sum * inv);
@@ -783,9 +791,9 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
   a.q_tile = kPwaRows / a.group_chunk;
   const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
   if ((int64_t)kv_heads * chunks > 65535) return TIB_E_SIZE;
-  // A step with a portion of a prompt in it runs on the tensor cores (bf16); single tokens, 32-bit, and head sizes
-  // that are no multiples of 8 run on the CUDA cores.
-  if (dtype == TIB_BF16 && !force_simt && (int64_t)max_q_len * a.group_chunk > 16 && pwa_mma_takes(a, q)) {
+  // bf16 steps run on the tensor cores, single tokens too (their tiles come in by cp.async, 16 bytes a piece, where the
+  // other kernel waits for one element at a time); 32-bit and head sizes that are no multiples of 8 run on the CUDA cores.
+  if (dtype == TIB_BF16 && !force_simt && pwa_mma_takes(a, q)) {
     if (dim <= 64 && vdim <= 64) return pwa_launch_mma<64, 64>(q, out, a, n_entries, max_q_len, stream);
     if (dim <= 64) return pwa_launch_mma<64, 128>(q, out, a, n_entries, max_q_len, stream);
     if (vdim <= 64) return pwa_launch_mma<128, 64>(q, out, a, n_entries, max_q_len, stream);

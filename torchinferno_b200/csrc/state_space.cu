@@ -110,9 +110,18 @@ __global__ void __launch_bounds__(kConvChannels) short_conv_kernel(ConvArgs a) {
 }
 
 // --------------------------------------------------------------------------------------------------- the scan
-constexpr int kScanLanesN = 8;         // lanes that share one column of the state along N
-constexpr int kScanCols = 16;          // columns (of P) a block of 128 threads owns
+// A block of 128 threads owns 16 * CP columns of one head's state: 8 lanes share a group of CP columns along N (lane l holds
+// n = l, l + 8, ...), so a token's B and C are read once from shared memory for CP columns.  A step whose longest portion
+// is at most one run walks every portion from its slot's state in one launch.  Longer portions are cut into runs of
+// kScanRun tokens that are walked side by side: first every run from a zero state (its own sum L_r and the product of its
+// decays A_r), then one thread per state element folds S_(r+1) = A_r S_r + L_r over the request's runs, leaving each run's
+// starting state in the place of its sum and the last state in the slot, then every run again from its starting state,
+// now with the outputs.  Cutting changes only the order of fp32 sums.
+constexpr int kScanLanesN = 8;         // lanes that share a column group along N
+constexpr int kScanGroups = 16;        // column groups of a block
 constexpr int kScanChunk = 16;         // tokens staged at a time
+constexpr int kScanRun = 64;           // tokens of a run
+enum { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
 struct ScanArgs {
   const void* xbc; int xbc_dtype; int64_t ld_xbc;        // rows [x: heads * P | B: groups * N | C: groups * N]
@@ -121,42 +130,57 @@ struct ScanArgs {
   float* state; int64_t state_stride;                      // per slot: S [heads][N][P] at offset 0
   const int* q_start; const int* slots;
   float* y;                                                // [tokens, heads * P] fp32
+  float* run_state; float* run_decay;                      // [runs][heads * N * P], [runs][heads]
   int heads, groups, N, P;
 };
 
-template <int NPT>
+// The first run of an entry in the run arrays: entries' runs never overlap, since an entry of len tokens has at most
+// len / kScanRun + 1 runs and the next entry starts len rows and one entry later.
+__device__ __forceinline__ size_t scan_first_run(int row0, int entry) { return (size_t)(row0 / kScanRun) + entry; }
+
+template <int NPT, int CP, int MODE>
 __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
   pdl_wait();
   pdl_trigger();
   constexpr int NP = NPT * kScanLanesN;                    // N padded
-  __shared__ float b_s[kScanChunk][NP], c_s[kScanChunk][NP], x_s[kScanChunk][kScanCols], dt_s[kScanChunk], a_s[kScanChunk];
-  const int entry = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * kScanCols;
-  const int row0 = a.q_start[entry], len = a.q_start[entry + 1] - row0;
-  if (len <= 0) return;
+  constexpr int COLS = kScanGroups * CP;
+  __shared__ float b_s[kScanChunk][NP], c_s[MODE == kScanLocal ? 1 : kScanChunk][NP];
+  __shared__ __align__(16) float x_s[kScanChunk][COLS];
+  __shared__ float dt_s[kScanChunk], a_s[kScanChunk];
+  const int entry = blockIdx.z;
   const int N = a.N, P = a.P, inner = a.heads * P;
+  const int tiles = (P + COLS - 1) / COLS;
+  const int h = blockIdx.x / tiles, p0 = (blockIdx.x - h * tiles) * COLS;
+  const int row0 = a.q_start[entry], len = a.q_start[entry + 1] - row0;
+  const int first = MODE == kScanWhole ? 0 : blockIdx.y * kScanRun;
+  if (first >= len) return;
+  const int last = MODE == kScanWhole ? len : min(len, first + kScanRun);
   const int g = h / (a.heads / a.groups);
-  const int ln = threadIdx.x % kScanLanesN, col = threadIdx.x / kScanLanesN;     // col 0..15
-  const int p = p0 + col;
-  const bool live = p < P;
-  float* S = a.state + (size_t)a.slots[entry] * a.state_stride + (size_t)h * N * P;
-  float s[NPT];
+  const int ln = threadIdx.x % kScanLanesN, cg = threadIdx.x / kScanLanesN;
+  const int p = p0 + cg * CP;                              // this thread's first column
+  const size_t run = scan_first_run(row0, entry) + blockIdx.y;
+  float* S = MODE == kScanWhole ? a.state + (size_t)a.slots[entry] * a.state_stride + (size_t)h * N * P
+                                : a.run_state + (run * a.heads + h) * (size_t)N * P;
+  float s[NPT][CP];
 #pragma unroll
   for (int j = 0; j < NPT; ++j) {
     const int n = ln + kScanLanesN * j;
-    s[j] = (live && n < N) ? S[(size_t)n * P + p] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CP; ++c) s[j][c] = (MODE != kScanLocal && p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
   }
   const float rate = expf(a.a_log[h]), bias = a.dt_bias[h], skip = a.d_skip[h];
-  for (int t0 = 0; t0 < len; t0 += kScanChunk) {
-    const int nt = min(kScanChunk, len - t0);
+  float kept = 1.f;                                        // the product of the run's decays
+  for (int t0 = first; t0 < last; t0 += kScanChunk) {
+    const int nt = min(kScanChunk, last - t0);
     __syncthreads();
     for (int e = threadIdx.x; e < nt * NP; e += blockDim.x) {
       const int t = e / NP, n = e - t * NP;
       const size_t row = (size_t)(row0 + t0 + t) * a.ld_xbc;
       b_s[t][n] = n < N ? ss_load(a.xbc, a.xbc_dtype, row + inner + g * N + n) : 0.f;
-      c_s[t][n] = n < N ? ss_load(a.xbc, a.xbc_dtype, row + inner + (a.groups + g) * N + n) : 0.f;
+      if (MODE != kScanLocal) c_s[t][n] = n < N ? ss_load(a.xbc, a.xbc_dtype, row + inner + (a.groups + g) * N + n) : 0.f;
     }
-    for (int e = threadIdx.x; e < nt * kScanCols; e += blockDim.x) {
-      const int t = e / kScanCols, cc = e - t * kScanCols;
+    for (int e = threadIdx.x; e < nt * COLS; e += blockDim.x) {
+      const int t = e / COLS, cc = e - t * COLS;
       x_s[t][cc] = p0 + cc < P ? ss_load(a.xbc, a.xbc_dtype, (size_t)(row0 + t0 + t) * a.ld_xbc + h * P + p0 + cc) : 0.f;
     }
     if (threadIdx.x < nt) {
@@ -166,26 +190,83 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
-      const float decay = a_s[t], x = x_s[t][col], dx = dt_s[t] * x;
-      float acc = 0.f;
+      const float decay = a_s[t], step = dt_s[t];
+      float x[CP], dx[CP], acc[CP];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        x[c] = x_s[t][cg * CP + c];
+        dx[c] = step * x[c];
+        acc[c] = 0.f;
+      }
+      kept *= decay;
 #pragma unroll
       for (int j = 0; j < NPT; ++j) {
         const int n = ln + kScanLanesN * j;
-        s[j] = fmaf(decay, s[j], dx * b_s[t][n]);
-        acc = fmaf(s[j], c_s[t][n], acc);
+        const float b = b_s[t][n];
+        if (MODE == kScanLocal) {
+#pragma unroll
+          for (int c = 0; c < CP; ++c) s[j][c] = fmaf(decay, s[j][c], dx[c] * b);
+        } else {
+          const float cn = c_s[t][n];
+#pragma unroll
+          for (int c = 0; c < CP; ++c) {
+            s[j][c] = fmaf(decay, s[j][c], dx[c] * b);
+            acc[c] = fmaf(s[j][c], cn, acc[c]);
+          }
+        }
       }
+      if (MODE != kScanLocal) {
 #pragma unroll
-      for (int o = kScanLanesN / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ln == 0 && live) a.y[(size_t)(row0 + t0 + t) * inner + h * P + p] = fmaf(skip, x, acc);
+        for (int c = 0; c < CP; ++c) {
+#pragma unroll
+          for (int o = kScanLanesN / 2; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+          if (ln == 0 && p + c < P) a.y[(size_t)(row0 + t0 + t) * inner + h * P + p + c] = fmaf(skip, x[c], acc[c]);
+        }
+      }
     }
   }
-  if (live) {
+  if (MODE == kScanFrom) return;
 #pragma unroll
-    for (int j = 0; j < NPT; ++j) {
-      const int n = ln + kScanLanesN * j;
-      if (n < N) S[(size_t)n * P + p] = s[j];
+  for (int j = 0; j < NPT; ++j) {
+    const int n = ln + kScanLanesN * j;
+#pragma unroll
+    for (int c = 0; c < CP; ++c)
+      if (p + c < P && n < N) S[(size_t)n * P + p + c] = s[j][c];
+  }
+  if (MODE == kScanLocal && p0 == 0 && threadIdx.x == 0) a.run_decay[run * a.heads + h] = kept;
+}
+
+// grid (state elements / 256, entries): S_(r+1) = A_r S_r + L_r over the entry's runs; run_state[r] turns from L_r into S_r.
+__global__ void __launch_bounds__(256) ssd_fold_runs_kernel(ScanArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int entry = blockIdx.y;
+  const int row0 = a.q_start[entry], len = a.q_start[entry + 1] - row0;
+  const size_t per_head = (size_t)a.N * a.P, width = per_head * a.heads;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (len <= 0 || e >= width) return;
+  const int h = (int)(e / per_head);
+  const int runs = (len + kScanRun - 1) / kScanRun;
+  const size_t run0 = scan_first_run(row0, entry);
+  float* slot = a.state + (size_t)a.slots[entry] * a.state_stride + e;
+  float st = *slot;
+  constexpr int AHEAD = 4;
+  for (int r = 0; r < runs; r += AHEAD) {
+    float sum[AHEAD], decay[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      const bool in = r + u < runs;
+      sum[u] = in ? a.run_state[(run0 + r + u) * width + e] : 0.f;
+      decay[u] = in ? a.run_decay[(run0 + r + u) * a.heads + h] : 1.f;
+    }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      if (r + u >= runs) break;
+      a.run_state[(run0 + r + u) * width + e] = st;
+      st = fmaf(decay[u], st, sum[u]);
     }
   }
+  *slot = st;
 }
 
 // -------------------------------------------------------------------------------------------- gate, then norm
@@ -236,31 +317,56 @@ TIB_API int tib_short_conv(const void* in, int in_dtype, int64_t ld, int col, co
   return TIB_OK;
 }
 
-// The largest state size N the scan takes.
+// The largest state size N the scan takes, and the length of a run.
 TIB_API int tib_ssd_scan_max_state() { return 32 * kScanLanesN; }
+TIB_API int tib_ssd_scan_run() { return kScanRun; }
 
+template <int NPT, int CP>
+static int ssd_scan_launch(const ScanArgs& a, int n_entries, int max_q_len, bool runs, cudaStream_t stream) {
+  const int tiles = ceil_div(a.P, kScanGroups * CP);
+  if (!runs) {
+    TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanWhole>), dim3(tiles * a.heads, 1, n_entries), 128, 0, stream, a);
+    return TIB_OK;
+  }
+  const dim3 grid(tiles * a.heads, ceil_div(max_q_len, kScanRun), n_entries);
+  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanLocal>), grid, 128, 0, stream, a);
+  const int64_t width = (int64_t)a.heads * a.N * a.P;
+  TIB_LAUNCH_DEPENDENT(ssd_fold_runs_kernel, dim3((unsigned)ceil_div64(width, 256), n_entries), 256, 0, stream, a);
+  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanFrom>), grid, 128, 0, stream, a);
+  return TIB_OK;
+}
+
+// run_state [run_capacity][heads * N * P] and run_decay [run_capacity][heads] (fp32, contents do not matter) are needed
+// when max_q_len exceeds a run: run_capacity >= n_tokens / run + n_entries.  Without them every portion is walked in
+// one piece.
 TIB_API int tib_ssd_scan(const void* xbc, int xbc_dtype, int64_t ld_xbc, const void* dt, int dt_dtype, int64_t ld_dt, int dt_col,
                          const float* dt_bias, const float* a_log, const float* d_skip, float* state, int64_t state_stride,
                          const int* q_start, const int* slots, float* y, int heads, int groups, int N, int P, int n_entries,
+                         int n_tokens, int max_q_len, float* run_state, float* run_decay, int64_t run_capacity,
                          cudaStream_t stream) {
-  if (n_entries == 0) return TIB_OK;
+  if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!xbc || !dt || !dt_bias || !a_log || !d_skip || !state || !q_start || !slots || !y) return TIB_E_ARG;
   if (heads < 1 || groups < 1 || heads % groups || N < 1 || P < 1 || N > 32 * kScanLanesN) return TIB_E_SIZE;
-  if (heads > 65535 || n_entries > 65535) return TIB_E_SIZE;
+  if (n_entries > 65535 || n_tokens < 0 || max_q_len < 0) return TIB_E_SIZE;
   if (!ss_known(xbc_dtype) || !ss_known(dt_dtype)) return TIB_E_DTYPE;
+  const bool runs = max_q_len > kScanRun && run_state && run_decay;
+  if (runs && (run_capacity < n_tokens / kScanRun + n_entries || ceil_div(max_q_len, kScanRun) > 65535)) return TIB_E_SIZE;
   ScanArgs a;
   a.xbc = xbc; a.xbc_dtype = xbc_dtype; a.ld_xbc = ld_xbc; a.dt = dt; a.dt_dtype = dt_dtype; a.ld_dt = ld_dt; a.dt_col = dt_col;
   a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.state = state; a.state_stride = state_stride;
-  a.q_start = q_start; a.slots = slots; a.y = y; a.heads = heads; a.groups = groups; a.N = N; a.P = P;
-  const dim3 grid(ceil_div(P, kScanCols), heads, n_entries);
+  a.q_start = q_start; a.slots = slots; a.y = y; a.run_state = run_state; a.run_decay = run_decay;
+  a.heads = heads; a.groups = groups; a.N = N; a.P = P;
   const int npt = ceil_div(N, kScanLanesN);
-  if (npt <= 2) TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<2>, grid, 128, 0, stream, a);
-  else if (npt <= 4) TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<4>, grid, 128, 0, stream, a);
-  else if (npt <= 6) TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<6>, grid, 128, 0, stream, a);
-  else if (npt <= 8) TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<8>, grid, 128, 0, stream, a);
-  else if (npt <= 16) TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<16>, grid, 128, 0, stream, a);
-  else TIB_LAUNCH_DEPENDENT(ssd_scan_kernel<32>, grid, 128, 0, stream, a);
-  return TIB_OK;
+  const bool wide = P > kScanGroups;        // four columns a thread where a head has more columns than a block has groups
+#define TIB_SCAN_CASE(NPT) \
+  return wide ? ssd_scan_launch<NPT, 4>(a, n_entries, max_q_len, runs, stream) : ssd_scan_launch<NPT, 1>(a, n_entries, max_q_len, runs, stream)
+  if (npt <= 2) TIB_SCAN_CASE(2);
+  if (npt <= 4) TIB_SCAN_CASE(4);
+  if (npt <= 6) TIB_SCAN_CASE(6);
+  if (npt <= 8) TIB_SCAN_CASE(8);
+  if (npt <= 16) TIB_SCAN_CASE(16);
+  TIB_SCAN_CASE(32);
+#undef TIB_SCAN_CASE
 }
 
 // y: [rows, width] fp32; z: rows of z_dtype (row stride ldz, first column z_col); weight [width] fp32; out [rows, width].

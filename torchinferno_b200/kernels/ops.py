@@ -125,7 +125,7 @@ def lib() -> ctypes.CDLL:
                    "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group", "tib_router_logits",
                    "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
                    "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence",
-                   "tib_softcap_f32", "tib_short_conv", "tib_ssd_scan", "tib_ssd_scan_max_state", "tib_gated_group_norm",
+                   "tib_softcap_f32", "tib_short_conv", "tib_ssd_scan", "tib_ssd_scan_max_state", "tib_ssd_scan_run", "tib_gated_group_norm",
                    "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
@@ -1224,12 +1224,25 @@ def ssd_scan_max_state() -> int:
     return int(lib().tib_ssd_scan_max_state())
 
 
+_scan_run: int | None = None
+
+
+def ssd_scan_run() -> int:
+    """How many tokens the scan walks in one piece when it cuts long portions."""
+    global _scan_run
+    if _scan_run is None:
+        _scan_run = int(lib().tib_ssd_scan_run())
+    return _scan_run
+
+
 def ssd_scan(xbc: torch.Tensor, dt_rows: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y: torch.Tensor, n_entries: int, *, heads: int,
-             groups: int, state_dim: int, head_dim: int) -> torch.Tensor:
+             groups: int, state_dim: int, head_dim: int, max_q_len: int | None = None) -> torch.Tensor:
     """The recurrence S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t per head over the ragged batch;
     ``xbc`` rows hold [x | B | C]; ``dt_rows[:, dt_col + h]`` the raw step size of head h; S is the first
-    heads * state_dim * head_dim floats of ``state[slot]`` (fp32), read at the start and left at the end."""
+    heads * state_dim * head_dim floats of ``state[slot]`` (fp32), read at the start and left at the end.
+    ``max_q_len``: the longest entry of the step; when it exceeds one run of the kernel, portions are cut into runs that
+    are walked side by side (scratch for the runs' states is allocated here); None: every portion in one piece."""
     _rows_of(xbc, "xbc", heads * head_dim + 2 * groups * state_dim), _rows_of(dt_rows, "dt_rows")
     _need(state, "state", torch.float32), _need(y, "y", torch.float32)
     for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
@@ -1239,10 +1252,18 @@ def ssd_scan(xbc: torch.Tensor, dt_rows: torch.Tensor, dt_col: int, dt_bias: tor
     if (y.shape != (xbc.shape[0], heads * head_dim) or dt_rows.shape[0] != xbc.shape[0] or dt_col < 0
             or dt_col + heads > dt_rows.shape[1] or state.dim() != 2 or state.shape[1] < heads * state_dim * head_dim):
         raise KernelError("ssd_scan: shapes do not fit")
+    n_tokens = xbc.shape[0]
+    run_state = run_decay = None
+    capacity = 0
+    if max_q_len is not None and max_q_len > ssd_scan_run():
+        capacity = n_tokens // ssd_scan_run() + n_entries
+        run_state = torch.empty((capacity, heads * state_dim * head_dim), dtype=torch.float32, device=xbc.device)
+        run_decay = torch.empty((capacity, heads), dtype=torch.float32, device=xbc.device)
     _check("ssd_scan", lib().tib_ssd_scan(
         _ptr(xbc), c_int(_code(xbc.dtype)), c_int64(xbc.stride(0)), _ptr(dt_rows), c_int(_code(dt_rows.dtype)),
         c_int64(dt_rows.stride(0)), c_int(dt_col), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), c_int64(state.stride(0)),
         _ptr(q_start), _ptr(slots), _ptr(y), c_int(heads), c_int(groups), c_int(state_dim), c_int(head_dim), c_int(n_entries),
+        c_int(n_tokens), c_int(n_tokens if max_q_len is None else max_q_len), _ptr(run_state), _ptr(run_decay), c_int64(capacity),
         _stream()))
     return y
 
@@ -1328,8 +1349,7 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
     with 0 <= i - j < window and the blocks b of ``pool`` positions with b * pool + pool - 1 <= i - window (their means K_b,
     V_b from the strided pages), scores q . k * scale * temp[h], exp(sink[h]) added to the denominator; turn_back undoes at
     position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone.
-    bfloat16 steps that hold a portion of a prompt run on the tensor cores when the head sizes are multiples of 8 up to
-    128, unless ``force_simt``."""
+    bfloat16 steps run on the tensor cores when the head sizes are multiples of 8 up to 128, unless ``force_simt``."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim = keys.shape[3], values.shape[3]
     n = q.shape[0]

@@ -90,7 +90,8 @@ class StateSpaceDuality(Mixer):
                        batch.q_start, batch.slots, xbc, batch.n_entries, batch.max_q_len, silu=True)
         y = torch.empty((n, inner), dtype=torch.float32, device=x.device)
         ops.ssd_scan(xbc, proj, inner + self.channels, self.dt_bias, self.a_log, self.d_skip, ctx.state, batch.q_start, batch.slots,
-                     y, batch.n_entries, heads=self.heads, groups=self.groups, state_dim=self.state_dim, head_dim=self.head_dim)
+                     y, batch.n_entries, heads=self.heads, groups=self.groups, state_dim=self.state_dim, head_dim=self.head_dim,
+                     max_q_len=batch.max_q_len)
         rows = torch.empty((n, inner), dtype=x.dtype, device=x.device)
         ops.gated_group_norm(y, proj, 0, self.norm_weight, self.eps, rows, self.norm_groups)
         return linear(rows, self.o_weight)
