@@ -124,11 +124,19 @@ struct PwaPoolArgs {
   int* error_word;
 };
 
-// grid (tokens, kv_heads); a block has work only where its token completes a block of `pool` positions
+// grid (tokens, kv_heads); a block has work only where its token completes a block of `pool` positions.  The block's
+// positions are dealt to kPoolLanes lanes (lane l sums l, l + lanes, ... in rising order, every load of a thread in
+// flight at once); then one thread per element adds the lanes' sums in the order of the lanes.  The order is the same
+// wherever the block is completed, in a prompt's portion or by a single token.
+constexpr int kPoolLanes = 8;
+constexpr int kPoolTile = 64;             // elements a lane's threads cover side by side
+constexpr int kPoolAhead = 8;             // loads a thread keeps in flight
+
 template <typename T>
-__global__ void __launch_bounds__(128) pwa_pool_kernel(PwaPoolArgs a) {
+__global__ void __launch_bounds__(kPoolLanes * kPoolTile) pwa_pool_kernel(PwaPoolArgs a) {
   pdl_wait();
   pdl_trigger();
+  __shared__ float part_s[kPoolLanes][kPoolTile + 1];
   const int t = blockIdx.x, kvh = blockIdx.y;
   const int pos = a.positions[t];
   if (pos % a.pool != a.pool - 1) return;
@@ -139,27 +147,40 @@ __global__ void __launch_bounds__(128) pwa_pool_kernel(PwaPoolArgs a) {
   if (bpage < 0) return;
   const int width = a.dim + a.vdim;
   const float inv = 1.f / (float)a.pool;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    const bool is_k = e < a.dim;
+  const int lane = threadIdx.x / kPoolTile, col = threadIdx.x % kPoolTile;
+  bool bad = false;
+  for (int e0 = 0; e0 < width; e0 += kPoolTile) {
+    const int e = e0 + col;
+    const bool live = e < width, is_k = e < a.dim;
     const int dd = is_k ? e : e - a.dim, w = is_k ? a.dim : a.vdim;
     const T* base = reinterpret_cast<const T*>(is_k ? a.tokens.keys : a.tokens.values);
     float sum = 0.f;
-    constexpr int AHEAD = 8;              // loads in flight; the sum still runs in rising order of position
-    for (int j0 = 0; j0 < a.pool; j0 += AHEAD) {
-      float part[AHEAD];
+    for (int j0 = lane; j0 < a.pool; j0 += kPoolLanes * kPoolAhead) {
+      float got[kPoolAhead];
 #pragma unroll
-      for (int u = 0; u < AHEAD; ++u) {
-        const int j = j0 + u;
-        const int page = j < a.pool ? pwa_page(a.tokens, ttable, first + j, a.error_word, 0x50000 + (t & 0xffff)) : -1;
-        part[u] = page < 0 ? 0.f
-                           : to_f32(base[(size_t)page * a.tokens.page_stride + ((size_t)kvh * a.tokens.page_size + (first + j) % a.tokens.page_size) * w + dd]);
+      for (int u = 0; u < kPoolAhead; ++u) {
+        const int j = j0 + u * kPoolLanes;
+        got[u] = 0.f;
+        if (!live || j >= a.pool) continue;
+        const int page = ttable[(first + j) / a.tokens.page_size];
+        if (page < 0 || page >= a.tokens.num_pages) { bad = true; continue; }
+        got[u] = to_f32(base[(size_t)page * a.tokens.page_stride + ((size_t)kvh * a.tokens.page_size + (first + j) % a.tokens.page_size) * w + dd]);
       }
 #pragma unroll
-      for (int u = 0; u < AHEAD; ++u) sum += part[u];
+      for (int u = 0; u < kPoolAhead; ++u) sum += got[u];
     }
-    T* out = reinterpret_cast<T*>(is_k ? a.blocks.keys : a.blocks.values);
-    out[(size_t)bpage * a.blocks.page_stride + ((size_t)kvh * a.blocks.page_size + b % a.blocks.page_size) * w + dd] = from_f32<T>(sum * inv);
+    __syncthreads();
+    part_s[lane][col] = sum;
+    __syncthreads();
+    if (lane == 0 && live) {
+      float total = 0.f;
+#pragma unroll
+      for (int l = 0; l < kPoolLanes; ++l) total += part_s[l][col];
+      T* out = reinterpret_cast<T*>(is_k ? a.blocks.keys : a.blocks.values);
+      out[(size_t)bpage * a.blocks.page_stride + ((size_t)kvh * a.blocks.page_size + b % a.blocks.page_size) * w + dd] = from_f32<T>(total * inv);
+    }
   }
+  if (bad && a.error_word) atomicExch(a.error_word, 0x50000 + (t & 0xffff));
 }
 
 // ------------------------------------------------------------------------------------------------- attention
@@ -756,8 +777,8 @@ TIB_API int tib_pool_blocks(const void* k_pages, const void* v_pages, const int*
   a.blocks = pwa_cache(bk_pages, bv_pages, b_table, b_table_stride, b_page_size, b_page_stride, b_num_pages);
   a.error_word = error_word;
   const dim3 grid(n_tokens, kv_heads);
-  if (dtype == TIB_F32) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<float>, grid, 128, 0, stream, a);
-  else if (dtype == TIB_BF16) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<__nv_bfloat16>, grid, 128, 0, stream, a);
+  if (dtype == TIB_F32) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<float>, grid, kPoolLanes * kPoolTile, 0, stream, a);
+  else if (dtype == TIB_BF16) TIB_LAUNCH_DEPENDENT(pwa_pool_kernel<__nv_bfloat16>, grid, kPoolLanes * kPoolTile, 0, stream, a);
   else return TIB_E_DTYPE;
   return TIB_OK;
 }
