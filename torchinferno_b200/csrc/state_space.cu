@@ -117,10 +117,14 @@ __global__ void __launch_bounds__(kConvChannels) short_conv_kernel(ConvArgs a) {
 // decays A_r), then one thread per state element folds S_(r+1) = A_r S_r + L_r over the request's runs, leaving each run's
 // starting state in the place of its sum and the last state in the slot, then every run again from its starting state,
 // now with the outputs.  Cutting changes only the order of fp32 sums.
+//
+// Tokens are staged in shared memory a chunk at a time, in two stages: while the block walks token t of one chunk, its
+// threads fetch row t of the next chunk into registers (as raw bits, so that nothing waits on the loads) and leave it in
+// the other stage after the token's arithmetic.  A row of a stage is [(B_n, C_n) pairs: NP | x: COLS | step, decay].
 constexpr int kScanLanesN = 8;         // lanes that share a column group along N
 constexpr int kScanGroups = 16;        // column groups of a block
-constexpr int kScanChunk = 16;         // tokens staged at a time
 constexpr int kScanRun = 64;           // tokens of a run
+constexpr int kScanThreads = 128;
 enum { kScanWhole = 0, kScanLocal = 1, kScanFrom = 2 };
 
 struct ScanArgs {
@@ -138,15 +142,23 @@ struct ScanArgs {
 // len / kScanRun + 1 runs and the next entry starts len rows and one entry later.
 __device__ __forceinline__ size_t scan_first_run(int row0, int entry) { return (size_t)(row0 / kScanRun) + entry; }
 
+__device__ __forceinline__ unsigned ss_load_raw(const void* p, int dtype, size_t i) {
+  return dtype == TIB_F32 ? reinterpret_cast<const unsigned*>(p)[i] : (unsigned)reinterpret_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float ss_from_raw(unsigned raw, int dtype) { return __uint_as_float(dtype == TIB_F32 ? raw : raw << 16); }
+
 template <int NPT, int CP, int MODE>
-__global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   pdl_wait();
   pdl_trigger();
   constexpr int NP = NPT * kScanLanesN;                    // N padded
   constexpr int COLS = kScanGroups * CP;
-  __shared__ float b_s[kScanChunk][NP], c_s[MODE == kScanLocal ? 1 : kScanChunk][NP];
-  __shared__ __align__(16) float x_s[kScanChunk][COLS];
-  __shared__ float dt_s[kScanChunk], a_s[kScanChunk];
+  constexpr int CHUNK = NPT <= 16 ? 16 : 8;                // tokens of a stage
+  constexpr int ROW = 2 * NP + COLS;                       // values fetched for a token
+  constexpr int FETCH = (ROW + kScanThreads - 1) / kScanThreads;
+  __shared__ __align__(16) float2 bc_s[2][CHUNK][NP];
+  __shared__ __align__(16) float x_s[2][CHUNK][COLS];
+  __shared__ float dt_s[2][CHUNK], a_s[2][CHUNK];
   const int entry = blockIdx.z;
   const int N = a.N, P = a.P, inner = a.heads * P;
   const int tiles = (P + COLS - 1) / COLS;
@@ -156,7 +168,8 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
   if (first >= len) return;
   const int last = MODE == kScanWhole ? len : min(len, first + kScanRun);
   const int g = h / (a.heads / a.groups);
-  const int ln = threadIdx.x % kScanLanesN, cg = threadIdx.x / kScanLanesN;
+  const int tid = threadIdx.x;
+  const int ln = tid % kScanLanesN, cg = tid / kScanLanesN;
   const int p = p0 + cg * CP;                              // this thread's first column
   const size_t run = scan_first_run(row0, entry) + blockIdx.y;
   float* S = MODE == kScanWhole ? a.state + (size_t)a.slots[entry] * a.state_stride + (size_t)h * N * P
@@ -169,32 +182,76 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
     for (int c = 0; c < CP; ++c) s[j][c] = (MODE != kScanLocal && p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
   }
   const float rate = expf(a.a_log[h]), bias = a.dt_bias[h], skip = a.d_skip[h];
-  float kept = 1.f;                                        // the product of the run's decays
-  for (int t0 = first; t0 < last; t0 += kScanChunk) {
-    const int nt = min(kScanChunk, last - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * NP; e += blockDim.x) {
-      const int t = e / NP, n = e - t * NP;
-      const size_t row = (size_t)(row0 + t0 + t) * a.ld_xbc;
-      b_s[t][n] = n < N ? ss_load(a.xbc, a.xbc_dtype, row + inner + g * N + n) : 0.f;
-      if (MODE != kScanLocal) c_s[t][n] = n < N ? ss_load(a.xbc, a.xbc_dtype, row + inner + (a.groups + g) * N + n) : 0.f;
+  const int xdt = a.xbc_dtype;
+
+  // what this thread fetches of a token's row: for piece i the column of the input row (-1: nothing, the place holds
+  // zero) and the float of the stage's row it lands in
+  int src[FETCH], dst[FETCH];
+#pragma unroll
+  for (int i = 0; i < FETCH; ++i) {
+    const int col = i * kScanThreads + tid;
+    src[i] = -1;
+    dst[i] = -1;
+    if (col < NP) {                                        // B_n
+      dst[i] = 2 * col;
+      if (col < N) src[i] = inner + g * N + col;
+    } else if (col < 2 * NP) {                             // C_n
+      const int n = col - NP;
+      if (MODE != kScanLocal) {
+        dst[i] = 2 * n + 1;
+        if (n < N) src[i] = inner + (a.groups + g) * N + n;
+      }
+    } else if (col < ROW) {                                // x
+      const int cc = col - 2 * NP;
+      dst[i] = 2 * NP * CHUNK + cc;                        // (told apart from the pairs below)
+      if (p0 + cc < P) src[i] = h * P + p0 + cc;
     }
-    for (int e = threadIdx.x; e < nt * COLS; e += blockDim.x) {
-      const int t = e / COLS, cc = e - t * COLS;
-      x_s[t][cc] = p0 + cc < P ? ss_load(a.xbc, a.xbc_dtype, (size_t)(row0 + t0 + t) * a.ld_xbc + h * P + p0 + cc) : 0.f;
-    }
-    if (threadIdx.x < nt) {
-      const float step = ss_softplus(ss_load(a.dt, a.dt_dtype, (size_t)(row0 + t0 + threadIdx.x) * a.ld_dt + a.dt_col + h) + bias);
-      dt_s[threadIdx.x] = step;
-      a_s[threadIdx.x] = expf(-rate * step);
-    }
-    __syncthreads();
+  }
+  auto put = [&](int stage, int t, int i, float v) {
+    if (dst[i] < 0) return;
+    if (dst[i] >= 2 * NP * CHUNK) x_s[stage][t][dst[i] - 2 * NP * CHUNK] = v;
+    else reinterpret_cast<float*>(&bc_s[stage][t][0])[dst[i]] = v;
+  };
+  auto put_step = [&](int stage, int t, float raw) {
+    const float step = ss_softplus(raw + bias);
+    dt_s[stage][t] = step;
+    a_s[stage][t] = expf(-rate * step);
+  };
+
+  // the first chunk, all at once
+  {
+    const int nt = min(CHUNK, last - first);
     for (int t = 0; t < nt; ++t) {
-      const float decay = a_s[t], step = dt_s[t];
+      const size_t row = (size_t)(row0 + first + t) * a.ld_xbc;
+#pragma unroll
+      for (int i = 0; i < FETCH; ++i) put(0, t, i, src[i] >= 0 ? ss_from_raw(ss_load_raw(a.xbc, xdt, row + src[i]), xdt) : 0.f);
+    }
+    if (tid < nt) put_step(0, tid, ss_load(a.dt, a.dt_dtype, (size_t)(row0 + first + tid) * a.ld_dt + a.dt_col + h));
+  }
+  __syncthreads();
+
+  float kept = 1.f;                                        // the product of the run's decays
+  int stage = 0;
+  for (int t0 = first; t0 < last; t0 += CHUNK, stage ^= 1) {
+    const int nt = min(CHUNK, last - t0);
+    const int nt_next = min(CHUNK, last - t0 - CHUNK);     // (at most 0 after the last chunk)
+    for (int t = 0; t < nt; ++t) {
+      // row t of the next chunk: the loads are issued now and their values used after this token's arithmetic
+      const bool fetch = t < nt_next;
+      const bool step_mine = fetch && tid == (t & 3) * 32;
+      unsigned raw[FETCH];
+      float raw_step = 0.f;
+      if (fetch) {
+        const size_t row = (size_t)(row0 + t0 + CHUNK + t) * a.ld_xbc;
+#pragma unroll
+        for (int i = 0; i < FETCH; ++i) raw[i] = src[i] >= 0 ? ss_load_raw(a.xbc, xdt, row + src[i]) : 0u;
+        if (step_mine) raw_step = ss_load(a.dt, a.dt_dtype, (size_t)(row0 + t0 + CHUNK + t) * a.ld_dt + a.dt_col + h);
+      }
+      const float decay = a_s[stage][t], step = dt_s[stage][t];
       float x[CP], dx[CP], acc[CP];
 #pragma unroll
       for (int c = 0; c < CP; ++c) {
-        x[c] = x_s[t][cg * CP + c];
+        x[c] = x_s[stage][t][cg * CP + c];
         dx[c] = step * x[c];
         acc[c] = 0.f;
       }
@@ -202,16 +259,16 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
 #pragma unroll
       for (int j = 0; j < NPT; ++j) {
         const int n = ln + kScanLanesN * j;
-        const float b = b_s[t][n];
         if (MODE == kScanLocal) {
+          const float b = bc_s[stage][t][n].x;
 #pragma unroll
           for (int c = 0; c < CP; ++c) s[j][c] = fmaf(decay, s[j][c], dx[c] * b);
         } else {
-          const float cn = c_s[t][n];
+          const float2 bc = bc_s[stage][t][n];
 #pragma unroll
           for (int c = 0; c < CP; ++c) {
-            s[j][c] = fmaf(decay, s[j][c], dx[c] * b);
-            acc[c] = fmaf(s[j][c], cn, acc[c]);
+            s[j][c] = fmaf(decay, s[j][c], dx[c] * bc.x);
+            acc[c] = fmaf(s[j][c], bc.y, acc[c]);
           }
         }
       }
@@ -223,7 +280,13 @@ __global__ void __launch_bounds__(128) ssd_scan_kernel(ScanArgs a) {
           if (ln == 0 && p + c < P) a.y[(size_t)(row0 + t0 + t) * inner + h * P + p + c] = fmaf(skip, x[c], acc[c]);
         }
       }
+      if (fetch) {
+#pragma unroll
+        for (int i = 0; i < FETCH; ++i) put(stage ^ 1, t, i, ss_from_raw(raw[i], xdt));
+        if (step_mine) put_step(stage ^ 1, t, raw_step);
+      }
     }
+    __syncthreads();      // the next chunk is whole in its stage, and nobody reads this one any more
   }
   if (MODE == kScanFrom) return;
 #pragma unroll
@@ -325,14 +388,14 @@ template <int NPT, int CP>
 static int ssd_scan_launch(const ScanArgs& a, int n_entries, int max_q_len, bool runs, cudaStream_t stream) {
   const int tiles = ceil_div(a.P, kScanGroups * CP);
   if (!runs) {
-    TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanWhole>), dim3(tiles * a.heads, 1, n_entries), 128, 0, stream, a);
+    TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanWhole>), dim3(tiles * a.heads, 1, n_entries), kScanThreads, 0, stream, a);
     return TIB_OK;
   }
   const dim3 grid(tiles * a.heads, ceil_div(max_q_len, kScanRun), n_entries);
-  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanLocal>), grid, 128, 0, stream, a);
+  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanLocal>), grid, kScanThreads, 0, stream, a);
   const int64_t width = (int64_t)a.heads * a.N * a.P;
   TIB_LAUNCH_DEPENDENT(ssd_fold_runs_kernel, dim3((unsigned)ceil_div64(width, 256), n_entries), 256, 0, stream, a);
-  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanFrom>), grid, 128, 0, stream, a);
+  TIB_LAUNCH_DEPENDENT((ssd_scan_kernel<NPT, CP, kScanFrom>), grid, kScanThreads, 0, stream, a);
   return TIB_OK;
 }
 
