@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kConvChannels) short_conv_kernel(ConvArgs a) {
 
 // --------------------------------------------------------------------------------------------------- the scan
 // A block of 128 threads owns 16 * CP columns of one head's state: 8 lanes share a group of CP columns along N (lane l holds
-// n = l, l + 8, ...), so a token's B and C are read once from shared memory for CP columns.  A step whose longest portion
+// the pairs n = 2 l, 2 l + 1, then 16 further on and so on, two values to a 64-bit register for fma.rn.f32x2), so a token's B and C are read once from shared memory for CP columns.  A step whose longest portion
 // is at most one run walks every portion from its slot's state in one launch.  Longer portions are cut into runs of
 // kScanRun tokens that are walked side by side: first every run from a zero state (its own sum L_r and the product of its
 // decays A_r), then one thread per state element folds S_(r+1) = A_r S_r + L_r over the request's runs, leaving each run's
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kConvChannels) short_conv_kernel(ConvArgs a) {
 //
 // Tokens are staged in shared memory a chunk at a time, in two stages: while the block walks token t of one chunk, its
 // threads fetch row t of the next chunk into registers (as raw bits, so that nothing waits on the loads) and leave it in
-// the other stage after the token's arithmetic.  A row of a stage is [(B_n, C_n) pairs: NP | x: COLS | step, decay].
+// the other stage after the token's arithmetic.
 constexpr int kScanLanesN = 8;         // lanes that share a column group along N
 constexpr int kScanGroups = 16;        // column groups of a block
 constexpr int kScanRun = 64;           // tokens of a run
@@ -147,6 +147,26 @@ __device__ __forceinline__ unsigned ss_load_raw(const void* p, int dtype, size_t
 }
 __device__ __forceinline__ float ss_from_raw(unsigned raw, int dtype) { return __uint_as_float(dtype == TIB_F32 ? raw : raw << 16); }
 
+// Two fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100 (each half is rounded as the scalar
+// instruction rounds it).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <int NPT, int CP, int MODE>
 __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   pdl_wait();
@@ -156,7 +176,9 @@ __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   constexpr int CHUNK = NPT <= 16 ? 16 : 8;                // tokens of a stage
   constexpr int ROW = 2 * NP + COLS;                       // values fetched for a token
   constexpr int FETCH = (ROW + kScanThreads - 1) / kScanThreads;
-  __shared__ __align__(16) float2 bc_s[2][CHUNK][NP];
+  static_assert(NPT % 2 == 0, "a thread holds pairs of neighbouring n");
+  constexpr int NH = NPT / 2;
+  __shared__ __align__(16) float4 bc_s[2][CHUNK][NP / 2];   // (B_n, B_(n+1), C_n, C_(n+1)) for even n
   __shared__ __align__(16) float x_s[2][CHUNK][COLS];
   __shared__ float dt_s[2][CHUNK], a_s[2][CHUNK];
   const int entry = blockIdx.z;
@@ -174,12 +196,16 @@ __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   const size_t run = scan_first_run(row0, entry) + blockIdx.y;
   float* S = MODE == kScanWhole ? a.state + (size_t)a.slots[entry] * a.state_stride + (size_t)h * N * P
                                 : a.run_state + (run * a.heads + h) * (size_t)N * P;
-  float s[NPT][CP];
+  // this thread's n: 2 * ln + 16 * j and the one after it, as the halves of a pair
+  f32x2 s[NH][CP];
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) {
-    const int n = ln + kScanLanesN * j;
+  for (int j = 0; j < NH; ++j) {
+    const int n = 2 * ln + 2 * kScanLanesN * j;
 #pragma unroll
-    for (int c = 0; c < CP; ++c) s[j][c] = (MODE != kScanLocal && p + c < P && n < N) ? S[(size_t)n * P + p + c] : 0.f;
+    for (int c = 0; c < CP; ++c) {
+      const bool in = MODE != kScanLocal && p + c < P;
+      s[j][c] = f2_pack(in && n < N ? S[(size_t)n * P + p + c] : 0.f, in && n + 1 < N ? S[(size_t)(n + 1) * P + p + c] : 0.f);
+    }
   }
   const float rate = expf(a.a_log[h]), bias = a.dt_bias[h], skip = a.d_skip[h];
   const int xdt = a.xbc_dtype;
@@ -193,12 +219,12 @@ __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
     src[i] = -1;
     dst[i] = -1;
     if (col < NP) {                                        // B_n
-      dst[i] = 2 * col;
+      dst[i] = (col >> 1) * 4 + (col & 1);
       if (col < N) src[i] = inner + g * N + col;
     } else if (col < 2 * NP) {                             // C_n
       const int n = col - NP;
       if (MODE != kScanLocal) {
-        dst[i] = 2 * n + 1;
+        dst[i] = (n >> 1) * 4 + 2 + (n & 1);
         if (n < N) src[i] = inner + (a.groups + g) * N + n;
       }
     } else if (col < ROW) {                                // x
@@ -221,10 +247,20 @@ __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   // the first chunk, all at once
   {
     const int nt = min(CHUNK, last - first);
-    for (int t = 0; t < nt; ++t) {
-      const size_t row = (size_t)(row0 + first + t) * a.ld_xbc;
+    for (int tb = 0; tb < nt; tb += 4) {                   // four rows' loads in flight at a time
+      unsigned got[4][FETCH];
 #pragma unroll
-      for (int i = 0; i < FETCH; ++i) put(0, t, i, src[i] >= 0 ? ss_from_raw(ss_load_raw(a.xbc, xdt, row + src[i]), xdt) : 0.f);
+      for (int u = 0; u < 4; ++u) {
+        const size_t row = (size_t)(row0 + first + min(tb + u, nt - 1)) * a.ld_xbc;
+#pragma unroll
+        for (int i = 0; i < FETCH; ++i) got[u][i] = src[i] >= 0 ? ss_load_raw(a.xbc, xdt, row + src[i]) : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (tb + u >= nt) break;
+#pragma unroll
+        for (int i = 0; i < FETCH; ++i) put(0, tb + u, i, ss_from_raw(got[u][i], xdt));
+      }
     }
     if (tid < nt) put_step(0, tid, ss_load(a.dt, a.dt_dtype, (size_t)(row0 + first + tid) * a.ld_dt + a.dt_col + h));
   }
@@ -235,66 +271,90 @@ __global__ void __launch_bounds__(kScanThreads) ssd_scan_kernel(ScanArgs a) {
   for (int t0 = first; t0 < last; t0 += CHUNK, stage ^= 1) {
     const int nt = min(CHUNK, last - t0);
     const int nt_next = min(CHUNK, last - t0 - CHUNK);     // (at most 0 after the last chunk)
-    for (int t = 0; t < nt; ++t) {
-      // row t of the next chunk: the loads are issued now and their values used after this token's arithmetic
-      const bool fetch = t < nt_next;
-      const bool step_mine = fetch && tid == (t & 3) * 32;
-      unsigned raw[FETCH];
-      float raw_step = 0.f;
-      if (fetch) {
-        const size_t row = (size_t)(row0 + t0 + CHUNK + t) * a.ld_xbc;
+    // Row t of the next chunk is asked for when the walk reaches token t and put into the other stage two tokens later
+    // (the last two after the walk), so that nothing waits on the loads.
+    unsigned raw[2][FETCH];
+    float raw_step[2];
+    auto ask = [&](int t, unsigned (&r)[FETCH], float& rs) {
+      if (t >= nt_next) return;
+      const size_t row = (size_t)(row0 + t0 + CHUNK + t) * a.ld_xbc;
 #pragma unroll
-        for (int i = 0; i < FETCH; ++i) raw[i] = src[i] >= 0 ? ss_load_raw(a.xbc, xdt, row + src[i]) : 0u;
-        if (step_mine) raw_step = ss_load(a.dt, a.dt_dtype, (size_t)(row0 + t0 + CHUNK + t) * a.ld_dt + a.dt_col + h);
-      }
+      for (int i = 0; i < FETCH; ++i) r[i] = src[i] >= 0 ? ss_load_raw(a.xbc, xdt, row + src[i]) : 0u;
+      if (tid == (t & 3) * 32) rs = ss_load(a.dt, a.dt_dtype, (size_t)(row0 + t0 + CHUNK + t) * a.ld_dt + a.dt_col + h);
+    };
+    auto land = [&](int t, const unsigned (&r)[FETCH], float rs) {
+      if (t < 0 || t >= nt_next) return;
+#pragma unroll
+      for (int i = 0; i < FETCH; ++i) put(stage ^ 1, t, i, ss_from_raw(r[i], xdt));
+      if (tid == (t & 3) * 32) put_step(stage ^ 1, t, rs);
+    };
+    auto walk = [&](int t) {
       const float decay = a_s[stage][t], step = dt_s[stage][t];
-      float x[CP], dx[CP], acc[CP];
+      float x[CP], acc[CP];
+      f32x2 dx[CP], sum[CP];
+      const f32x2 decay2 = f2_pack(decay, decay);
 #pragma unroll
       for (int c = 0; c < CP; ++c) {
         x[c] = x_s[stage][t][cg * CP + c];
-        dx[c] = step * x[c];
-        acc[c] = 0.f;
+        const float d = step * x[c];
+        dx[c] = f2_pack(d, d);
+        sum[c] = f2_pack(0.f, 0.f);
       }
       kept *= decay;
 #pragma unroll
-      for (int j = 0; j < NPT; ++j) {
-        const int n = ln + kScanLanesN * j;
+      for (int j = 0; j < NH; ++j) {
+        const int pair = ln + kScanLanesN * j;
         if (MODE == kScanLocal) {
-          const float b = bc_s[stage][t][n].x;
+          const f32x2 b = reinterpret_cast<const ulonglong2*>(&bc_s[stage][t][pair])->x;
 #pragma unroll
-          for (int c = 0; c < CP; ++c) s[j][c] = fmaf(decay, s[j][c], dx[c] * b);
+          for (int c = 0; c < CP; ++c) s[j][c] = f2_fma(decay2, s[j][c], f2_mul(dx[c], b));
         } else {
-          const float2 bc = bc_s[stage][t][n];
+          const ulonglong2 bc = *reinterpret_cast<const ulonglong2*>(&bc_s[stage][t][pair]);
 #pragma unroll
           for (int c = 0; c < CP; ++c) {
-            s[j][c] = fmaf(decay, s[j][c], dx[c] * bc.x);
-            acc[c] = fmaf(s[j][c], bc.y, acc[c]);
+            s[j][c] = f2_fma(decay2, s[j][c], f2_mul(dx[c], bc.x));
+            sum[c] = f2_fma(s[j][c], bc.y, sum[c]);
           }
         }
       }
       if (MODE != kScanLocal) {
 #pragma unroll
         for (int c = 0; c < CP; ++c) {
+          float even, odd;
+          f2_unpack(sum[c], even, odd);
+          acc[c] = even + odd;
 #pragma unroll
           for (int o = kScanLanesN / 2; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
           if (ln == 0 && p + c < P) a.y[(size_t)(row0 + t0 + t) * inner + h * P + p + c] = fmaf(skip, x[c], acc[c]);
         }
       }
-      if (fetch) {
-#pragma unroll
-        for (int i = 0; i < FETCH; ++i) put(stage ^ 1, t, i, ss_from_raw(raw[i], xdt));
-        if (step_mine) put_step(stage ^ 1, t, raw_step);
+    };
+    for (int t = 0; t < nt; t += 2) {
+      land(t - 2, raw[0], raw_step[0]);
+      ask(t, raw[0], raw_step[0]);
+      walk(t);
+      if (t + 1 < nt) {
+        land(t - 1, raw[1], raw_step[1]);
+        ask(t + 1, raw[1], raw_step[1]);
+        walk(t + 1);
       }
     }
+    // (a chunk with a successor is full, so nt is even there and the rows still in registers are nt - 2 and nt - 1)
+    land(nt - 2, raw[0], raw_step[0]);
+    land(nt - 1, raw[1], raw_step[1]);
     __syncthreads();      // the next chunk is whole in its stage, and nobody reads this one any more
   }
   if (MODE == kScanFrom) return;
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) {
-    const int n = ln + kScanLanesN * j;
+  for (int j = 0; j < NH; ++j) {
+    const int n = 2 * ln + 2 * kScanLanesN * j;
 #pragma unroll
-    for (int c = 0; c < CP; ++c)
-      if (p + c < P && n < N) S[(size_t)n * P + p + c] = s[j][c];
+    for (int c = 0; c < CP; ++c) {
+      float lo, hi;
+      f2_unpack(s[j][c], lo, hi);
+      if (p + c < P && n < N) S[(size_t)n * P + p + c] = lo;
+      if (p + c < P && n + 1 < N) S[(size_t)(n + 1) * P + p + c] = hi;
+    }
   }
   if (MODE == kScanLocal && p0 == 0 && threadIdx.x == 0) a.run_decay[run * a.heads + h] = kept;
 }
