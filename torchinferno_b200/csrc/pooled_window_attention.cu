@@ -406,7 +406,7 @@ static int pwa_launch(const void* q, void* out, const PwaArgs& a, int n_entries,
 constexpr int kPmRows = 64, kPmKeys = 64, kPmThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DK, int DV>
+template <int DK, int DV, int ST, bool WT>
 __global__ void __launch_bounds__(kPmThreads)
 pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, PwaArgs a) {
   pdl_wait();
@@ -414,10 +414,10 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   constexpr int KP = DK + 8, VP = DV + 8;        // padded rows: ldmatrix rows fall in different banks
   extern __shared__ __align__(16) unsigned char sm_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);          // [64][KP]
-  __nv_bfloat16* k_s = q_s + kPmRows * KP;                                 // [2][64][KP]
-  __nv_bfloat16* v_s = k_s + 2 * kPmKeys * KP;                             // [2][64][VP]
-  __shared__ long long page_base[2][kPmKeys];
-  __shared__ int key_row[2][kPmKeys];
+  __nv_bfloat16* k_s = q_s + kPmRows * KP;                                 // [ST][64][KP]
+  __nv_bfloat16* v_s = k_s + ST * kPmKeys * KP;                            // [ST][64][VP]
+  __shared__ long long page_base[ST][kPmKeys];
+  __shared__ int key_row[ST][kPmKeys];
 
   const int d = a.dim, vd = a.vdim;
   const int entry = blockIdx.y;
@@ -446,25 +446,27 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int s_lo = first_key / kPmKeys, s_hi = last_pos / kPmKeys;
   const int steps = steps_b + (s_hi - s_lo + 1);
 
-  auto fetch = [&](int stage, int step) {
+  // where key j of a tile lives: its page's first element and its row in the page
+  auto locate = [&](int stage, int step, int j) {
     const bool pooled = step < steps_b;
     const PwaCache& c = pooled ? a.blocks : a.tokens;
-    // where every key of the tile lives, once: its page's first element and its row in the page
-    if (tid < kPmKeys) {
-      const int idx = (pooled ? step : s_lo + step - steps_b) * kPmKeys + tid;
-      long long base = -1;
-      int row = 0;
-      if (pooled ? idx < n_blocks : (idx <= last_pos && idx >= first_key)) {
-        const int page = pwa_page(c, pooled ? btable : ttable, idx, a.error_word, 0x10000 + entry);
-        if (page >= 0) {
-          base = (long long)page * c.page_stride;
-          row = kvh * c.page_size + idx % c.page_size;
-        }
+    const int idx = (pooled ? step : s_lo + step - steps_b) * kPmKeys + j;
+    long long base = -1;
+    int row = 0;
+    if (pooled ? idx < n_blocks : (idx <= last_pos && idx >= first_key)) {
+      const int page = pwa_page(c, pooled ? btable : ttable, idx, a.error_word, 0x10000 + entry);
+      if (page >= 0) {
+        base = (long long)page * c.page_stride;
+        row = kvh * c.page_size + idx % c.page_size;
       }
-      page_base[stage][tid] = base;
-      key_row[stage][tid] = row;
     }
-    __syncthreads();
+    page_base[stage][j] = base;
+    key_row[stage][j] = row;
+  };
+  // the tile's keys and values, row by row from where `locate` found them
+  auto copy = [&](int stage, int step) {
+    const bool pooled = step < steps_b;
+    const PwaCache& c = pooled ? a.blocks : a.tokens;
     const __nv_bfloat16* k_pages = reinterpret_cast<const __nv_bfloat16*>(c.keys);
     const __nv_bfloat16* v_pages = reinterpret_cast<const __nv_bfloat16*>(c.values);
     constexpr int KPIECES = DK / 8, VPIECES = DV / 8;
@@ -482,6 +484,11 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
     cp_async_commit();
   };
+  auto fetch = [&](int stage, int step) {
+    if (tid < kPmKeys) locate(stage, step, tid);
+    __syncthreads();
+    copy(stage, step);
+  };
 
   // queries: 16-byte pieces, rows past the tile's end and padding columns are zero
   {
@@ -494,11 +501,19 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
       cp_async16(q_s + (size_t)r * KP + cc, src, ok);
     }
   }
-  fetch(0, 0);            // (there is always the tile of the query's own position)
+  // ST - 1 tiles ahead (there is always the tile of the query's own position); every step commits one group, an empty
+  // one when no tile is left, so that the wait below always leaves the same number pending
+  if (!WT) {
+#pragma unroll
+    for (int s0 = 0; s0 < ST - 1; ++s0) {
+      if (s0 < steps) fetch(s0, s0);
+      else cp_async_commit();
+    }
+  }
 
   // this thread's two rows: g8 and g8 + 8 of the warp's sixteen
   const int g8 = lane >> 2, t4 = lane & 3;
-  const int row_base = warp * 16;
+  const int row_base = WT ? 0 : warp * 16;           // (WT: every warp holds the block's only sixteen rows)
   int qpos[2], lo[2], seen[2];
   float factor[2], m[2], l[2];
   bool live[2];
@@ -525,15 +540,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int warp_lo = max(0, warp_first - a.window + 1);
   const int warp_seen = a.pool > 0 ? max(0, warp_last - a.window + 1) / a.pool : 0;
 
-  for (int step = 0; step < steps; ++step) {
-    const int stage = step & 1;
-    if (step + 1 < steps) {
-      fetch(stage ^ 1, step + 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+  auto tile = [&](int stage, int step) {
     const bool pooled = step < steps_b;
     const int base = (pooled ? step : s_lo + step - steps_b) * kPmKeys;
     // (a warp whose rows see nothing of this tile still passes the barriers)
@@ -622,16 +629,97 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         }
       }
     }
-    __syncthreads();      // the stage is free for the fetch after next
+  };
+  if (WT) {
+    // Few rows: only one warp would have work.  So the four warps each take one tile of a round of four (all in flight
+    // at once), with sums of their own, which are added in the order of the warps afterwards.
+    static_assert(!WT || ST == kPmThreads / 32, "a stage a warp");
+    for (int first = 0; first < steps; first += ST) {
+      // (all of the round's page numbers are asked for at once, then all of its tiles)
+      for (int e = tid; e < ST * kPmKeys; e += kPmThreads)
+        if (first + e / kPmKeys < steps) locate(e / kPmKeys, first + e / kPmKeys, e % kPmKeys);
+      __syncthreads();
+#pragma unroll
+      for (int s0 = 0; s0 < ST; ++s0)
+        if (first + s0 < steps) copy(s0, first + s0);
+      cp_async_wait<0>();
+      __syncthreads();
+      if (first + warp < steps) tile(warp, first + warp);
+      __syncthreads();    // the stages are free for the next round
+    }
+  } else {
+    for (int step = 0; step < steps; ++step) {
+      const int stage = step % ST;
+      if (step + ST - 1 < steps) fetch((step + ST - 1) % ST, step + ST - 1);      // (the stage of the step before this one)
+      else cp_async_commit();
+      cp_async_wait<ST - 1>();
+      __syncthreads();
+      tile(stage, step);
+      __syncthreads();      // the stage is free for the next step's fetch
+    }
   }
 
+  if (WT) {
+    // every warp leaves its maxima, denominators and sums where warp 0's thread of the same lane finds them
+    constexpr int PER = DV / 2 + 4;                      // floats a thread leaves
+    float* part_s = reinterpret_cast<float*>(k_s);       // [warps][32][PER] over the stages
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    if (warp > 0) {
+      float* mine = part_s + ((size_t)warp * 32 + lane) * PER;
+      mine[0] = m[0], mine[1] = m[1], mine[2] = l[0], mine[3] = l[1];
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mine[4 + n * 4 + c] = o[n][c];
+    }
+    __syncthreads();
+    if (warp == 0) {
+      float top[2] = {m[0], m[1]};
+      for (int w = 1; w < kPmThreads / 32; ++w) {
+        const float* theirs = part_s + ((size_t)w * 32 + lane) * PER;
+        top[0] = fmaxf(top[0], theirs[0]);
+        top[1] = fmaxf(top[1], theirs[1]);
+      }
+      float keep[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        keep[h] = m[h] == -CUDART_INF_F ? 0.f : exp2f(m[h] - top[h]);
+        l[h] *= keep[h];
+        m[h] = top[h];
+      }
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] *= keep[c >> 1];
+      for (int w = 1; w < kPmThreads / 32; ++w) {
+        const float* theirs = part_s + ((size_t)w * 32 + lane) * PER;
+        float weight[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          weight[h] = theirs[h] == -CUDART_INF_F ? 0.f : exp2f(theirs[h] - top[h]);
+          l[h] = fmaf(theirs[2 + h], weight[h], l[h]);
+        }
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) o[n][c] = fmaf(theirs[4 + n * 4 + c], weight[c >> 1], o[n][c]);
+      }
+    }
+    __syncthreads();      // the partial sums are read: the place is free for the rows' sums
+  }
   // the rows' sums, divided by the softmax's denominator (with the number that has no key), into shared memory
   float* o_s = reinterpret_cast<float*>(k_s);           // [64][DV] floats over the key and value stages, which adjoin
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float sum = l[h];
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!WT) {                                           // (WT: already summed over the four lanes of a row)
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    }
     float inv = 0.f;
     if (live[h]) {
       const int r = row_base + g8 + 8 * h;
@@ -644,6 +732,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
       inv = exp2f(m[h] - top) / denom;
     }
     const int r = row_base + g8 + 8 * h;
+    if (WT && warp > 0) continue;                        // (warp 0 holds the rows' whole sums)
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) {
       o_s[(size_t)r * DV + n * 8 + 2 * t4] = o[n][2 * h] * inv;
@@ -689,23 +778,33 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   }
 }
 
-template <int DK, int DV>
-static int pwa_launch_mma(const void* q, void* out, PwaArgs a, int n_entries, int max_q_len, cudaStream_t stream) {
-  static_assert(kPmRows * DV * sizeof(float) <= 2 * kPmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the rows' sums fit the stages");
-  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kPmRows * (DK + 8) + 2 * (size_t)kPmKeys * (DK + 8) + 2 * (size_t)kPmKeys * (DV + 8));
-  auto kern = pwa_attention_mma_kernel<DK, DV>;
+template <int DK, int DV, int ST, bool WT>
+static int pwa_launch_mma_staged(const void* q, void* out, const PwaArgs& a, dim3 grid, cudaStream_t stream) {
+  static_assert(kPmRows * DV * sizeof(float) <= ST * kPmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the rows' sums fit the stages");
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kPmRows * (DK + 8) + ST * (size_t)kPmKeys * (DK + 8) + ST * (size_t)kPmKeys * (DV + 8));
+  auto kern = pwa_attention_mma_kernel<DK, DV, ST, WT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
+  TIB_LAUNCH_DEPENDENT(kern, grid, kPmThreads, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, a);
+  return TIB_OK;
+}
+
+// In a step whose blocks all have at most sixteen rows (single tokens, say) one warp of four would have work while it
+// walks a dozen tiles one after the other: there the warps take a tile each, four tiles in flight at once, and their
+// sums are added afterwards in a fixed order.  A row's result then differs from the other form's in the order of fp32
+// sums only.
+template <int DK, int DV>
+static int pwa_launch_mma(const void* q, void* out, PwaArgs a, int n_entries, int max_q_len, cudaStream_t stream) {
   const int group = a.heads / a.kv_heads;
   a.group_chunk = group < kPmRows ? group : kPmRows;
   a.q_tile = kPmRows / a.group_chunk;
   const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
   if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
   const dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, a.kv_heads * chunks);
-  TIB_LAUNCH_DEPENDENT(kern, grid, kPmThreads, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, a);
-  return TIB_OK;
+  if ((int64_t)max_q_len * a.group_chunk <= 16) return pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+  return pwa_launch_mma_staged<DK, DV, 2, false>(q, out, a, grid, stream);
 }
 
 // Whether the tensor-core kernel takes these shapes (bf16; rows of 16-byte pieces in every array it copies from).
