@@ -393,10 +393,7 @@ __global__ void __launch_bounds__(256) ssd_fold_runs_kernel(ScanArgs a) {
 }
 
 // -------------------------------------------------------------------------------------------- gate, then norm
-// grid (rows, parts): out[t, c] = v / sqrt(mean over the part of v^2 + eps) * weight[c],  v = y[t, c] * silu(z[t, c]).
-// A thread keeps its first kNormKeep values in registers (all of them for parts of up to kNormKeep * blockDim columns), with
-// their loads in flight together; what a longer part has beyond is made again in the second pass.
-constexpr int kNormKeep = 16;
+// grid (rows, parts): out[t, c] = v / sqrt(mean over the part of v^2 + eps) * weight[c],  v = y[t, c] * silu(z[t, c])
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const void* __restrict__ z, int z_dtype, int64_t ldz, int z_col,
                         const float* __restrict__ weight, float eps, void* __restrict__ out, int out_dtype, int width, int part) {
@@ -405,31 +402,13 @@ gated_group_norm_kernel(const float* __restrict__ y, const void* __restrict__ z,
   __shared__ float scratch[33];
   const size_t row = blockIdx.x;
   const int c0 = blockIdx.y * part;
-  const int bd = blockDim.x;
-  float yv[kNormKeep], zv[kNormKeep], keep[kNormKeep];
-#pragma unroll
-  for (int i = 0; i < kNormKeep; ++i) {
-    const int c = threadIdx.x + i * bd;
-    yv[i] = c < part ? y[row * width + c0 + c] : 0.f;
-    zv[i] = c < part ? ss_load(z, z_dtype, row * ldz + z_col + c0 + c) : 0.f;
-  }
   float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < kNormKeep; ++i) {
-    keep[i] = yv[i] * ss_silu(zv[i]);
-    ss = fmaf(keep[i], keep[i], ss);
-  }
-  for (int c = threadIdx.x + kNormKeep * bd; c < part; c += bd) {
+  for (int c = threadIdx.x; c < part; c += blockDim.x) {
     const float v = y[row * width + c0 + c] * ss_silu(ss_load(z, z_dtype, row * ldz + z_col + c0 + c));
     ss = fmaf(v, v, ss);
   }
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)part + eps);
-#pragma unroll
-  for (int i = 0; i < kNormKeep; ++i) {
-    const int c = threadIdx.x + i * bd;
-    if (c < part) ss_store(out, out_dtype, row * width + c0 + c, keep[i] * inv * weight[c0 + c]);
-  }
-  for (int c = threadIdx.x + kNormKeep * bd; c < part; c += bd) {
+  for (int c = threadIdx.x; c < part; c += blockDim.x) {
     const float v = y[row * width + c0 + c] * ss_silu(ss_load(z, z_dtype, row * ldz + z_col + c0 + c));
     ss_store(out, out_dtype, row * width + c0 + c, v * inv * weight[c0 + c]);
   }
