@@ -631,11 +631,11 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
   };
   if (WT) {
-    // Few rows: only one warp would have work.  So the four warps each take one tile of a round of four (all in flight
+    // Few rows: only one warp would have work.  So the four warps each take one tile of a set of four (all in flight
     // at once), with sums of their own, which are added in the order of the warps afterwards.
     static_assert(!WT || ST == kPmThreads / 32, "a stage a warp");
     for (int first = 0; first < steps; first += ST) {
-      // (all of the round's page numbers are asked for at once, then all of its tiles)
+      // (all of the set's page numbers are asked for at once, then all of its tiles)
       for (int e = tid; e < ST * kPmKeys; e += kPmThreads)
         if (first + e / kPmKeys < steps) locate(e / kPmKeys, first + e / kPmKeys, e % kPmKeys);
       __syncthreads();
@@ -645,7 +645,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
       cp_async_wait<0>();
       __syncthreads();
       if (first + warp < steps) tile(warp, first + warp);
-      __syncthreads();    // the stages are free for the next round
+      __syncthreads();    // the stages are free for the next set
     }
   } else {
     for (int step = 0; step < steps; ++step) {
