@@ -269,7 +269,10 @@ def _run_portions(mixer, cache, name, x, portions, release=True):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,size,pool,page", [
     (4, 2, 16, 24, 20, 6, 8), (3, 1, 40, 8, 7, 3, 4), (2, 2, 64, 64, 33, 16, 16), (2, 1, 8, 4, 5, 1, 2), (1, 1, 12, 6, 4, 9, 4),
-    (6, 2, 32, 32, 16, 16, 16)])
+    (6, 2, 32, 32, 16, 16, 16),
+    # sixteen and eight query heads on one key head: a single token, or a portion of two, fills the sixteen rows up to
+    # which the warps of the tensor-core kernel take a tile each
+    (16, 1, 16, 16, 9, 4, 8), (8, 1, 24, 8, 70, 5, 16)])
 def test_pooled_window_attention_alone_at_the_edges_of_windows_blocks_and_pages(dtype, heads, kv_heads, dim, vdim, size, pool, page):
     """A prompt in portions, then single tokens, in a pool whose pages were used before and go back as the window passes.
     Some tokens carry values thirty times the usual size, and whole blocks do: a query that sees a token one step too long
