@@ -118,4 +118,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_LOADED:
         return
     _BUILTIN_LOADED = True
-    from torchinferno_b200.models import giforax, llama, tibalorn, zipedra  # noqa: F401
+    from torchinferno_b200.models import giforax, llama, tibalorn, vofidra, zipedra  # noqa: F401

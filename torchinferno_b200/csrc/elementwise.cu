@@ -145,12 +145,12 @@ add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* __restrict__ delta, float* __rest
 // Plain RMSNorm of rows held in type T (for parts that norm something other
 // than the residual stream, e.g. per-head norms).
 template <typename T>
-__global__ void rmsnorm_t_kernel(const T* __restrict__ x, const float* __restrict__ weight,
+__global__ void rmsnorm_t_kernel(const T* __restrict__ x, int64_t ldx, const float* __restrict__ weight,
                                  T* __restrict__ out, int hidden, float eps) {
   pdl_wait();
   pdl_trigger();
   __shared__ float scratch[33];
-  const T* src = x + (size_t)blockIdx.x * hidden;
+  const T* src = x + (size_t)blockIdx.x * ldx;
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     const float h = to_f32(src[c]);
@@ -307,15 +307,16 @@ TIB_API int tib_add_rmsnorm(const void* delta, float* residual, const int* rows,
   return TIB_OK;
 }
 
-TIB_API int tib_rmsnorm(const void* x, const float* weight, void* out, int n_rows, int hidden,
+// x: rows of `hidden` elements, ldx elements apart (a column slice of a wider row is fine); out: [n_rows, hidden]
+TIB_API int tib_rmsnorm(const void* x, int64_t ldx, const float* weight, void* out, int n_rows, int hidden,
                         float eps, int dtype, cudaStream_t stream) {
   if (n_rows == 0) return TIB_OK;
   if (!x || !weight || !out || n_rows < 0 || hidden < 1) return TIB_E_ARG;
   const int threads = norm_threads(hidden);
   if (dtype == TIB_F32)
-    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<float>, n_rows, threads, 0, stream, (const float*)x, weight, (float*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<float>, n_rows, threads, 0, stream, (const float*)x, ldx, weight, (float*)out, hidden, eps);
   else if (dtype == TIB_BF16)
-    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)x, ldx, weight, (__nv_bfloat16*)out, hidden, eps);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();

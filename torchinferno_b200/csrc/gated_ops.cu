@@ -55,10 +55,11 @@ __global__ void unit_norm_add_kernel(float* __restrict__ residual, const void* _
     residual[row * width + c] += load_any(y, y_dtype, row * ldy + c) * inv * weight[c];
 }
 
-// out[t] = f(x[t]) * sigmoid(g[t]);  f = identity (weight null) or the RMS norm with `weight`.
+// out[t] = f(x[t]) * sigmoid(g[t]);  f = identity (weight null) or the RMS norm with `weight`.  Column c reads gate
+// c / group: one gate per element (group 1) or one per run of `group` columns (a head).
 __global__ void sigmoid_gate_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, const void* __restrict__ g,
                                     int g_dtype, int64_t ldg, const float* __restrict__ weight, float eps,
-                                    void* __restrict__ out, int out_dtype, int width) {
+                                    void* __restrict__ out, int out_dtype, int width, int group) {
   pdl_wait();
   pdl_trigger();
   __shared__ float scratch[33];
@@ -75,7 +76,7 @@ __global__ void sigmoid_gate_kernel(const void* __restrict__ x, int x_dtype, int
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = load_any(x, x_dtype, row * ldx + c) * inv;
     if (weight) v *= weight[c];
-    store_any(out, out_dtype, row * width + c, v * sigmoid_f(load_any(g, g_dtype, row * ldg + c)));
+    store_any(out, out_dtype, row * width + c, v * sigmoid_f(load_any(g, g_dtype, row * ldg + (group > 1 ? c / group : c))));
   }
 }
 
@@ -178,13 +179,13 @@ TIB_API int tib_unit_norm_add(float* residual, const void* y, int y_dtype, int64
 }
 
 TIB_API int tib_sigmoid_gate(const void* x, int x_dtype, int64_t ldx, const void* g, int g_dtype, int64_t ldg,
-                             const float* weight, float eps, void* out, int out_dtype, int rows, int width,
+                             const float* weight, float eps, void* out, int out_dtype, int rows, int width, int group,
                              cudaStream_t stream) {
   if (rows == 0 || width == 0) return TIB_OK;
-  if (!x || !g || !out || rows < 0 || width < 0) return TIB_E_ARG;
+  if (!x || !g || !out || rows < 0 || width < 0 || group < 1) return TIB_E_ARG;
   if (!known(x_dtype) || !known(g_dtype) || !known(out_dtype)) return TIB_E_DTYPE;
   TIB_LAUNCH_DEPENDENT(sigmoid_gate_kernel, rows, row_threads(width), 0, stream, x, x_dtype, ldx, g, g_dtype, ldg, weight, eps,
-                       out, out_dtype, width);
+                       out, out_dtype, width, group);
   return TIB_OK;
 }
 

@@ -38,6 +38,7 @@ struct LatentAppendArgs {
   int64_t page_stride;
   float eps;
   int* error_word;
+  int half_pairs;             // 0: rotary pairs are (2i, 2i + 1); 1: (i, i + n_freq)
 };
 
 template <typename T>
@@ -67,7 +68,29 @@ __global__ void latent_append_kernel(const T* __restrict__ dkv, const T* __restr
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)a.rank + a.eps);
   if (dst)
     for (int c = threadIdx.x; c < a.rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32(src[c]) * inv * a.norm_weight[c]);
-  // the shared key part (job 0) and every head's rotated query part (jobs 1 .. heads): pairs (2i, 2i + 1)
+  // the shared key part (job 0) and every head's rotated query part (jobs 1 .. heads)
+  if (a.half_pairs) {
+    // pairs (i, i + n_freq) over the first 2 * n_freq elements; the rest pass unchanged
+    for (int e = threadIdx.x; e < (a.heads + 1) * a.rot; e += blockDim.x) {
+      const int job = e / a.rot, i = e - job * a.rot;
+      if (i >= a.n_freq && i < 2 * a.n_freq) continue;       // (written with its partner)
+      const T* from = job == 0 ? src + a.rank : q + t * a.ld_q + (size_t)(job - 1) * (a.dim + a.rot) + a.dim;
+      float* f = job == 0 ? nullptr : folded + (t * a.heads + (job - 1)) * (size_t)width + a.rank;
+      if (i < a.n_freq) {
+        const float lo = to_f32(from[i]), hi = to_f32(from[i + a.n_freq]);
+        const float angle = (float)pos * a.inv_freq[i];
+        const float c = cosf(angle), sn = sinf(angle);
+        const float l2 = rope_lo(lo, hi, c, sn), h2 = rope_hi(lo, hi, c, sn);
+        if (f) { f[i] = l2; f[i + a.n_freq] = h2; }
+        else if (dst) { dst[a.rank + i] = from_f32<T>(l2); dst[a.rank + i + a.n_freq] = from_f32<T>(h2); }
+      } else {
+        if (f) f[i] = to_f32(from[i]);
+        else if (dst) dst[a.rank + i] = from[i];
+      }
+    }
+    return;
+  }
+  // pairs (2i, 2i + 1)
   const int half = a.rot / 2;      // an odd last element, if any, passes unchanged below
   for (int e = threadIdx.x; e < (a.heads + 1) * half; e += blockDim.x) {
     const int job = e / half, i = e - job * half;
@@ -557,12 +580,13 @@ using namespace tib;
 
 // dkv: [tokens, rank + rot] (row stride ld_dkv); q: [tokens, heads * (dim + rot)] (row stride ld_q); pool: this layer's
 // pages, each [page_size][rank + rot] (null: nothing is stored); folded: [tokens, heads, rank + rot] fp32, of which
-// this call writes the last `rot` elements of every head.
+// this call writes the last `rot` elements of every head.  half_pairs: the rotary pairs are (i, i + n_freq) instead of
+// (2i, 2i + 1).
 TIB_API int tib_latent_append(const void* dkv, int64_t ld_dkv, const void* q, int64_t ld_q, void* pool, float* folded,
                               const int* positions, const int* token_slot, const int* block_table, int table_stride,
                               const float* norm_weight, float eps, const float* inv_freq, int n_freq, int n_tokens, int heads,
                               int dim, int rank, int rot, int page_size, int64_t page_stride, int num_pages,
-                              int* error_word, int dtype, cudaStream_t stream) {
+                              int half_pairs, int* error_word, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return TIB_OK;
   if (!dkv || !q || !folded || !positions || !norm_weight || (n_freq > 0 && !inv_freq)) return TIB_E_ARG;
   if (pool && (!token_slot || !block_table || page_size < 1)) return TIB_E_ARG;
@@ -571,7 +595,7 @@ TIB_API int tib_latent_append(const void* dkv, int64_t ld_dkv, const void* q, in
   a.positions = positions; a.token_slot = token_slot; a.block_table = block_table; a.table_stride = table_stride;
   a.norm_weight = norm_weight; a.inv_freq = inv_freq; a.n_freq = n_freq; a.rank = rank; a.rot = rot; a.heads = heads;
   a.dim = dim; a.ld_dkv = ld_dkv; a.ld_q = ld_q; a.page_size = page_size; a.num_pages = num_pages;
-  a.page_stride = page_stride; a.eps = eps; a.error_word = error_word;
+  a.page_stride = page_stride; a.eps = eps; a.error_word = error_word; a.half_pairs = half_pairs;
   if (dtype == TIB_F32)
     TIB_LAUNCH_DEPENDENT(latent_append_kernel<float>, n_tokens, 128, 0, stream, (const float*)dkv, (const float*)q,
                          (float*)pool, folded, a);

@@ -4,18 +4,20 @@
 //
 //   moe_route    from fp32 router logits [tokens, ld]: softmax over the experts (or sigmoid), the `top` largest
 //                scores (lowest index first among equals), their weights = score / (sum of the chosen + norm_eps)
-//                (or the bare scores), all fp32
+//                (or the bare scores), all fp32; optionally a correction per expert that counts for the choice only, and
+//                groups of neighbouring experts of which only the best few may be chosen from
 //   moe_group    counting sort of the tokens * top pairs by expert: offsets [experts + 1], order[sorted] = pair,
 //                place[pair] = sorted index.  The order inside an expert may differ from run to run; every row
 //                of a product is computed by itself, so no value depends on it
 //   moe_expert_product   y[s] = act(x[src(s)] . W_e^T) for the sorted rows s of expert e; W: [experts, n, k];
 //                act: none, relu^2, silu, or a clamped gated unit over (gate, up) row pairs of W (row 2i = gate i,
 //                row 2i + 1 = up i): g = min(g, limit), u = clamp(u, -limit, limit), y_i = g * sigmoid(alpha * g) * (u + 1),
-//                which leaves n / 2 columns.  `row_scale` (per pair, may be null) multiplies the fp32 sums before the
+//                or the plain gated unit y_i = silu(g) * u over the same pairs; either leaves n / 2 columns.  `row_scale` (per pair, may be null) multiplies the fp32 sums before the
 //                activation: a router weight that belongs on the expert's input.  bf16 operands whose rows are 16-byte aligned run on the tensor cores
 //                (mma.sync m16n8k16, fp32 accumulation, cp.async double buffering); everything else, and the
 //                32-bit path, on fp32 FMAs in fixed k order
-//   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t]); weights may be null (1)
+//   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t]); weights may be null (1);
+//                a choice whose id is `identity_from` or above has no expert: it adds weight * x[t], the input itself
 #include "mma.cuh"
 
 namespace tib {
@@ -85,12 +87,21 @@ router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restr
 }
 
 // ------------------------------------------------------------------- route
-__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int experts, int top, int sigmoid_scores,
-                                 int normalize, float norm_eps, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
+// One warp per token.  score(e) = softmax(z)[e] or sigmoid(z[e]); the choice looks at score + correction[e] (when a
+// correction is given) and, with `groups` > 1, only at the experts of the `keep` groups of neighbours whose largest
+// choice score is best (an expert of another group cannot be chosen, whatever its score); the weights are made from the
+// scores without the correction.  Lowest index first among equals, for groups and for experts.
+constexpr int kRouteMaxGroups = 64;      // (two groups a lane)
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int64_t ld, int experts, int top, int sigmoid_scores,
+                 int normalize, float norm_eps, const float* __restrict__ correction, int groups, int keep,
+                 int* __restrict__ ids, float* __restrict__ weights, int tokens) {
   pdl_wait();
   pdl_trigger();
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  __shared__ unsigned char kept_s[4][kRouteMaxGroups];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= tokens) return;
   const float* z = logits + (size_t)t * ld;
   float mx = -CUDART_INF_F;
@@ -99,25 +110,65 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
   float sum = 0.f;
   for (int e = lane; e < experts; e += 32) sum += expf(z[e] - mx);
   sum = warp_sum(sum);
+  auto score = [&](int e) { return sigmoid_scores ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum; };
+  const bool grouped = groups > 1 && keep < groups;
+  const int per_group = grouped ? experts / groups : experts;
+  if (grouped) {
+    float gscore[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int g = lane + 32 * i;
+      gscore[i] = -CUDART_INF_F;
+      if (g < groups) {
+        kept_s[warp][g] = 0;
+        for (int e = g * per_group; e < (g + 1) * per_group; ++e)
+          gscore[i] = fmaxf(gscore[i], score(e) + (correction ? correction[e] : 0.f));
+      }
+    }
+    __syncwarp();
+    unsigned taken = 0u;
+    for (int k = 0; k < keep; ++k) {
+      float best = -CUDART_INF_F;
+      int best_g = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int g = lane + 32 * i;
+        if (g < groups && !((taken >> i) & 1u) && (gscore[i] > best || best_g == 0x7fffffff)) { best = gscore[i]; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+      }
+      if (best_g < groups) {
+        if ((best_g & 31) == lane) { taken |= 1u << (best_g >> 5); kept_s[warp][best_g] = 1; }
+      }
+    }
+    __syncwarp();
+  }
   float chosen_sum = 0.f;
   unsigned long long taken_lo = 0ull;    // lane-local mask over this lane's experts (e = lane + 32 * i, i < 64)
   for (int k = 0; k < top; ++k) {
-    float best = -CUDART_INF_F;
+    float best = -CUDART_INF_F, best_s = 0.f;
     int best_e = 0x7fffffff;
     for (int e = lane, i = 0; e < experts; e += 32, ++i) {
       if ((taken_lo >> i) & 1ull) continue;
-      const float s = sigmoid_scores ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum;
-      if (s > best) { best = s; best_e = e; }     // (rising e: the lowest index wins among equals)
+      if (grouped && !kept_s[warp][e / per_group]) continue;
+      const float s = score(e);
+      const float c = s + (correction ? correction[e] : 0.f);
+      if (c > best || best_e == 0x7fffffff) { best = c; best_s = s; best_e = e; }     // (rising e: the lowest index wins among equals)
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_s = os; best_e = oe; }
     }
     if ((best_e & 31) == lane && best_e < experts) taken_lo |= 1ull << (best_e >> 5);
-    chosen_sum += best;
-    if (lane == 0) { ids[(size_t)t * top + k] = best_e; weights[(size_t)t * top + k] = best; }
+    chosen_sum += best_s;
+    if (lane == 0) { ids[(size_t)t * top + k] = best_e < experts ? best_e : -1; weights[(size_t)t * top + k] = best_e < experts ? best_s : 0.f; }
   }
   __syncwarp();
   if (normalize && lane < top) weights[(size_t)t * top + lane] /= (chosen_sum + norm_eps);
@@ -160,7 +211,7 @@ moe_group_kernel(const int* __restrict__ ids, int pairs, int experts, int* __res
 
 // ---------------------------------------------------------------- products
 constexpr int GM = 64, GN = 64, GK = 16;
-enum MoeAct : int { MOE_ACT_NONE = 0, MOE_ACT_RELU2 = 1, MOE_ACT_SILU = 2, MOE_ACT_GLU_CLAMP = 3 };
+enum MoeAct : int { MOE_ACT_NONE = 0, MOE_ACT_RELU2 = 1, MOE_ACT_SILU = 2, MOE_ACT_GLU_CLAMP = 3, MOE_ACT_SWIGLU = 4 };
 
 struct MoeEpilogue {
   int act;
@@ -173,7 +224,9 @@ __device__ __forceinline__ float moe_act(float v, int act) {
   if (act == MOE_ACT_SILU) return v / (1.f + expf(-v));
   return v;
 }
-__device__ __forceinline__ float moe_glu_clamp(float g, float u, float limit, float alpha) {
+// the gated units over (gate, up) row pairs: clamped (see above), or silu(g) * u
+__device__ __forceinline__ float moe_gated(float g, float u, int act, float limit, float alpha) {
+  if (act == MOE_ACT_SWIGLU) return g / (1.f + expf(-g)) * u;
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g / (1.f + expf(-alpha * g)) * (u + 1.f);
@@ -246,12 +299,12 @@ moe_expert_product_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __res
     const int r = ty * 4 + i;
     if (r >= rows) continue;
     const float rs = ep.row_scale ? ep.row_scale[order[first + r]] : 1.f;
-    if (ep.act == MOE_ACT_GLU_CLAMP) {
+    if (ep.act >= MOE_ACT_GLU_CLAMP) {
 #pragma unroll
       for (int j = 0; j < 4; j += 2) {
         const int gn = n0 + tx * 4 + j;
         if (gn + 1 >= N) continue;
-        y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_glu_clamp(acc[i][j] * rs, acc[i][j + 1] * rs, ep.limit, ep.alpha));
+        y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_gated(acc[i][j] * rs, acc[i][j + 1] * rs, ep.act, ep.limit, ep.alpha));
       }
       continue;
     }
@@ -357,9 +410,9 @@ moe_expert_product_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, 
         const int gn = n0 + wn + j * 8 + 2 * t + (c & 1);
         if (r >= rows || gn >= N) continue;
         const float rs = ep.row_scale ? ep.row_scale[order[first + r]] : 1.f;
-        if (ep.act == MOE_ACT_GLU_CLAMP) {      // (columns 2t and 2t + 1 of a tile sit in one thread: c and c + 1)
+        if (ep.act >= MOE_ACT_GLU_CLAMP) {      // (columns 2t and 2t + 1 of a tile sit in one thread: c and c + 1)
           if ((c & 1) == 0 && gn + 1 < N)
-            y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_glu_clamp(acc[i][j][c] * rs, acc[i][j][c + 1] * rs, ep.limit, ep.alpha));
+            y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_gated(acc[i][j][c] * rs, acc[i][j][c + 1] * rs, ep.act, ep.limit, ep.alpha));
           continue;
         }
         y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(moe_act(acc[i][j][c] * rs, ep.act));
@@ -370,7 +423,8 @@ moe_expert_product_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, 
 template <typename TS, typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
                                    int top, const TS* __restrict__ shared, const float* __restrict__ gate, int64_t ld_gate,
-                                   TO* __restrict__ out, int width) {
+                                   TO* __restrict__ out, int width, const int* __restrict__ ids, int identity_from,
+                                   const TO* __restrict__ x, int64_t ldx) {
   pdl_wait();
   pdl_trigger();
   const size_t t = blockIdx.x;
@@ -380,6 +434,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (int k = 0; k < top; ++k) {
       const int s = place[t * top + k];
       if (s >= 0) v = fmaf(weights ? weights[t * top + k] : 1.f, y[(size_t)s * width + c], v);
+      else if (ids && ids[t * top + k] >= identity_from) v = fmaf(weights ? weights[t * top + k] : 1.f, to_f32(x[t * ldx + c]), v);
     }
     if (shared) v = fmaf(g, to_f32(shared[t * width + c]), v);
     out[t * width + c] = from_f32<TO>(v);
@@ -412,13 +467,18 @@ TIB_API int tib_router_logits(const void* x, int x_dtype, int64_t ldx, const flo
   return TIB_OK;
 }
 
+// correction: [experts] fp32 added to the scores for the choice only, or null; groups > 1 with keep < groups: the experts
+// form `groups` equal runs of neighbours and only those of the best `keep` runs can be chosen.
 TIB_API int tib_moe_route(const float* logits, int64_t ld, int tokens, int experts, int top, int sigmoid_scores, int normalize,
-                          float norm_eps, int* ids, float* weights, cudaStream_t stream) {
+                          float norm_eps, const float* correction, int groups, int keep, int* ids, float* weights,
+                          cudaStream_t stream) {
   if (tokens == 0) return TIB_OK;
   if (!logits || !ids || !weights) return TIB_E_ARG;
   if (experts < 1 || experts > 2048 || top < 1 || top > experts) return TIB_E_SIZE;
+  if (groups < 1 || keep < 1 || keep > groups || groups > kRouteMaxGroups || experts % groups) return TIB_E_SIZE;
+  if (groups > 1 && keep < groups && top > keep * (experts / groups)) return TIB_E_SIZE;
   TIB_LAUNCH_DEPENDENT(moe_route_kernel, ceil_div(tokens, 4), 128, 0, stream, logits, ld, experts, top, sigmoid_scores, normalize,
-                       norm_eps, ids, weights, tokens);
+                       norm_eps, correction, groups, keep, ids, weights, tokens);
   return TIB_OK;
 }
 
@@ -437,7 +497,7 @@ TIB_API int tib_moe_expert_product(const void* x, int x_dtype, int64_t ldx, cons
                                    cudaStream_t stream) {
   if (pairs == 0 || N == 0) return TIB_OK;
   if (!x || !w || !y || !offsets || !order || pairs < 0 || N < 0 || K < 1 || top < 1) return TIB_E_ARG;
-  if (act < MOE_ACT_NONE || act > MOE_ACT_GLU_CLAMP || (act == MOE_ACT_GLU_CLAMP && N % 2)) return TIB_E_SIZE;
+  if (act < MOE_ACT_NONE || act > MOE_ACT_SWIGLU || (act >= MOE_ACT_GLU_CLAMP && N % 2)) return TIB_E_SIZE;
   MoeEpilogue ep;
   ep.act = act; ep.limit = limit; ep.alpha = alpha; ep.row_scale = row_scale;
   const int row_tiles = ceil_div(pairs, GM) + experts;      // at most this many tiles hold a row
@@ -466,18 +526,19 @@ TIB_API int tib_moe_expert_product(const void* x, int x_dtype, int64_t ldx, cons
 }
 
 // y: [pairs, width] fp32; shared: [tokens, width] in shared_dtype or null; gate: fp32 logit per token (stride ld_gate) or
-// null (the shared rows are added as they are); out: [tokens, width] in out_dtype.
+// null (the shared rows are added as they are); out: [tokens, width] in out_dtype.  ids [tokens * top] with identity_from
+// and x (the experts' input rows, in out_dtype, ldx elements apart): choices of id >= identity_from add weight * x[t].
 TIB_API int tib_moe_combine(const float* y, const int* place, const float* weights, int top, const void* shared,
                             int shared_dtype, const float* gate, int64_t ld_gate, void* out, int out_dtype, int tokens,
-                            int width, cudaStream_t stream) {
+                            int width, const int* ids, int identity_from, const void* x, int64_t ldx, cudaStream_t stream) {
   if (tokens == 0 || width == 0) return TIB_OK;
-  if (!y || !place || !out || top < 1) return TIB_E_ARG;
+  if (!y || !place || !out || top < 1 || (ids && !x)) return TIB_E_ARG;
   const int threads = width >= 1024 ? 256 : 128;
   // (few tokens: a row's columns are spread over several blocks)
   const dim3 grid(tokens, tokens < 2 * 148 ? ceil_div(width, threads) : 1);
 #define TIB_COMBINE_GO(TS, TO)                                                                                       \
   TIB_LAUNCH_DEPENDENT((moe_combine_kernel<TS, TO>), grid, threads, 0, stream, y, place, weights, top, (const TS*)shared, gate, \
-                       ld_gate, (TO*)out, width)
+                       ld_gate, (TO*)out, width, ids, identity_from, (const TO*)x, ldx)
   const int sd = shared ? shared_dtype : out_dtype;
   if (sd == TIB_F32 && out_dtype == TIB_F32) TIB_COMBINE_GO(float, float);
   else if (sd == TIB_BF16 && out_dtype == TIB_BF16) TIB_COMBINE_GO(__nv_bfloat16, __nv_bfloat16);

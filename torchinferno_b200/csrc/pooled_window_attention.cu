@@ -197,6 +197,7 @@ struct PwaArgs {
   const float* temp; const float* sink;                    // [heads] or null
   const float* vfreq;                                      // [vdim / 2] or null (values were not turned)
   const void* gate; int gate_dtype; int64_t ld_gate;       // [tokens, heads * vdim] logits or null
+  const float* rel_bias; int rel_span;                     // [heads, rel_span] or null: added to a token's score by distance
   PwaCache tokens, blocks;
   int group_chunk, q_tile;
   int* error_word;
@@ -305,6 +306,8 @@ pwa_attention_kernel(const T* __restrict__ q, T* __restrict__ out, PwaArgs a) {
       const float* kr = k_s + lane * (d + 1);
       for (int dd = 0; dd < d; ++dd) s = fmaf(qr[dd], kr[dd], s);
       s = allowed ? s * factor[i] : -CUDART_INF_F;
+      if (a.rel_bias && allowed && !pooled)           // a learned number per head and distance (the last entry serves all beyond)
+        s += a.rel_bias[(size_t)(kvh * group + g0 + r % gc) * a.rel_span + min(qpos - idx, a.rel_span - 1)];
       const float m_new = fmaxf(m[i], warp_max(s));   // finite: the step holds a key the row sees
       const float alpha = m[i] == -CUDART_INF_F ? 0.f : expf(m[i] - m_new);
       const float p = allowed ? expf(s - m_new) : 0.f;
@@ -517,6 +520,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   int qpos[2], lo[2], seen[2];
   float factor[2], m[2], l[2];
   bool live[2];
+  const float* rel[2];               // the row's head's biases by distance, or null
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = row_base + g8 + 8 * h;
@@ -526,6 +530,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     lo[h] = max(0, qpos[h] - a.window + 1);
     seen[h] = a.pool > 0 ? lo[h] / a.pool : 0;       // blocks 0 .. seen - 1 lie wholly behind the window
     factor[h] = a.scale * (a.temp ? a.temp[kvh * group + g0 + g] : 1.f) * kLog2e;
+    rel[h] = a.rel_bias ? a.rel_bias + (size_t)(kvh * group + g0 + g) * a.rel_span : nullptr;
     m[h] = -CUDART_INF_F;
     l[h] = 0.f;
   }
@@ -574,6 +579,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
           const int idx = base + n * 8 + 2 * t4 + (c & 1);
           const bool allowed = live[h] && (pooled ? idx < seen[h] : (idx <= qpos[h] && idx >= lo[h]));
           s[n][c] = allowed ? s[n][c] * factor[h] : -CUDART_INF_F;
+          if (rel[h] && allowed && !pooled) s[n][c] = fmaf(rel[h][min(qpos[h] - idx, a.rel_span - 1)], kLog2e, s[n][c]);
         }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -884,6 +890,8 @@ TIB_API int tib_pool_blocks(const void* k_pages, const void* v_pages, const int*
 
 // q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, heads * vdim] logits (row stride ld_gate, its
 // own dtype) or null; temp, sink: [heads] fp32 or null; vfreq: [vdim / 2] fp32 or null.  pool 0: the window alone.
+// rel_bias: [heads, rel_span] fp32 or null: rel_bias[h, min(i - j, rel_span - 1)] is added to the score of token j (not
+// multiplied by scale or temp; blocks get none).
 // force_simt: the CUDA-core kernel also where the tensor-core kernel would take the step.
 TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_start, const int* kv_start, const int* slots,
                                         const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
@@ -892,17 +900,19 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
                                         int64_t b_page_stride, int b_num_pages, int n_entries, int max_q_len, int heads,
                                         int kv_heads, int dim, int vdim, int window, int pool, float scale, const float* temp,
                                         const float* sink, const float* vfreq, const void* gate, int gate_dtype, int64_t ld_gate,
-                                        int* error_word, int dtype, int force_simt, cudaStream_t stream) {
+                                        const float* rel_bias, int rel_span, int* error_word, int dtype, int force_simt,
+                                        cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!q || !out || !q_start || !kv_start || !slots || !k_pages || !v_pages || !block_table) return TIB_E_ARG;
   if (pool > 0 && (!bk_pages || !bv_pages || !b_table || b_page_size < 1)) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || vdim < 1 || page_size < 1 || window < 1 || pool < 0) return TIB_E_SIZE;
   if (dim > 256 || vdim > 256 || (vfreq && vdim % 2) || n_entries > 65535) return TIB_E_SIZE;
   if (gate && gate_dtype != TIB_F32 && gate_dtype != TIB_BF16) return TIB_E_DTYPE;
+  if (rel_bias && rel_span < 1) return TIB_E_SIZE;
   PwaArgs a;
   a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim;
   a.window = window; a.pool = pool; a.scale = scale; a.temp = temp; a.sink = sink; a.vfreq = vfreq; a.gate = gate;
-  a.gate_dtype = gate_dtype; a.ld_gate = ld_gate;
+  a.gate_dtype = gate_dtype; a.ld_gate = ld_gate; a.rel_bias = rel_bias; a.rel_span = rel_span;
   a.tokens = pwa_cache(const_cast<void*>(k_pages), const_cast<void*>(v_pages), block_table, table_stride, page_size, page_stride, num_pages);
   a.blocks = pwa_cache(const_cast<void*>(bk_pages), const_cast<void*>(bv_pages), b_table, b_table_stride, b_page_size, b_page_stride, b_num_pages);
   a.error_word = error_word;

@@ -11,7 +11,8 @@
 //
 //   qk_norm_append     rotary encoding of part of every q and k head (pairs (i, i + rot/2) or (2i, 2i + 1), angles
 //                      fp32 position x fp32 frequency), then x / sqrt(mean(x^2) + eps) over the head (eps < 0: no
-//                      norm), all fp32; q goes to q_out, k and v (v untouched) into their page
+//                      norm), optionally times a weight per element and, for q, a temperature that grows with the
+//                      logarithm of the position, all fp32; q goes to q_out, k and v (v untouched) into their page
 //   sigmoid_attention  CUDA cores, every size: one warp owns a (token, head) row and walks the keys in blocks of 32
 //                      aligned to absolute positions in rising order, so a row's sums are the same whatever the
 //                      batch holds and however the prompt was cut.  The 32-bit path.
@@ -35,6 +36,8 @@ struct QkAppendArgs {
   const float* inv_freq;
   int page_size; int64_t page_stride; int num_pages;
   int* error_word;
+  const float* q_weight; const float* k_weight;     // [dim] each or null: multiply the normed head (one weight for all heads)
+  float temp_coef; int temp_every;                  // temp_every > 0: q times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
 };
 
 template <typename T>
@@ -92,8 +95,13 @@ qk_norm_append_kernel(const T* __restrict__ proj, T* __restrict__ q_out, T* __re
     T* dst = nullptr;
     if (is_q) dst = q_out + (size_t)tok * a.heads * a.dim + h * a.dim;
     else if (page >= 0) dst = k_pages + (size_t)page * a.page_stride + ((size_t)h * a.page_size + off) * a.dim;
-    if (dst)
-      for (int d = lane; d < a.dim; d += 32) dst[d] = from_f32<T>(head[d] * inv);
+    const float* weight = is_q ? a.q_weight : a.k_weight;
+    // the query's temperature grows with the logarithm of its position, in steps of temp_every positions
+    const float temp = (is_q && a.temp_every > 0) ? 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f) : 1.f;
+    if (dst) {
+      if (weight) for (int d = lane; d < a.dim; d += 32) dst[d] = from_f32<T>(head[d] * inv * weight[d] * temp);
+      else for (int d = lane; d < a.dim; d += 32) dst[d] = from_f32<T>(head[d] * inv * temp);
+    }
     __syncwarp();
   }
   if (write && page >= 0) {
@@ -573,12 +581,15 @@ static bool sigmoid_mma_takes(int dim, int vdim, int64_t page_stride, const void
 using namespace tib;
 
 // proj: [n_tokens, ld] rows holding q at q_off, k at k_off, v at v_off (k_off < 0: no k, v: nothing is stored);
-// q_out: [n_tokens, heads * dim]; k_pages / v_pages: first key / value of this layer's first page.
+// q_out: [n_tokens, heads * dim]; k_pages / v_pages: first key / value of this layer's first page.  q_weight / k_weight:
+// [dim] fp32 or null, multiplied into every normed head; temp_every > 0: every q is also multiplied by
+// 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1).
 TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_off, int v_off, void* q_out, void* k_pages,
                                void* v_pages, const int* positions, const int* token_slot, const int* block_table,
                                int table_stride, const float* inv_freq, int n_tokens, int heads, int kv_heads, int dim,
                                int vdim, int rot_dim, int interleaved, float eps, int page_size, int64_t page_stride,
-                               int num_pages, int* error_word, int dtype, cudaStream_t stream) {
+                               int num_pages, const float* q_weight, const float* k_weight, float temp_coef, int temp_every,
+                               int* error_word, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return TIB_OK;
   if (!proj || !q_out || !positions || n_tokens < 0 || heads < 1 || dim < 1) return TIB_E_ARG;
   if (rot_dim < 0 || rot_dim % 2 || rot_dim > dim || (rot_dim > 0 && !inv_freq)) return TIB_E_SIZE;
@@ -589,6 +600,7 @@ TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_of
   a.vdim = vdim; a.rot_dim = rot_dim; a.interleaved = interleaved; a.eps = eps; a.positions = positions;
   a.token_slot = token_slot; a.block_table = block_table; a.table_stride = table_stride; a.inv_freq = inv_freq;
   a.page_size = page_size; a.page_stride = page_stride; a.num_pages = num_pages; a.error_word = error_word;
+  a.q_weight = q_weight; a.k_weight = k_weight; a.temp_coef = temp_coef; a.temp_every = temp_every;
   const int rot_heads = heads + (k_off >= 0 ? kv_heads : 0);
   const int threads = 32 * (rot_heads < 4 ? 4 : rot_heads > 16 ? 16 : rot_heads);      // a warp a head, up to sixteen
   const size_t smem = sizeof(float) * ((size_t)rot_dim + (size_t)(threads / 32) * dim);

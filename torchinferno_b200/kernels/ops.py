@@ -126,7 +126,7 @@ def lib() -> ctypes.CDLL:
                    "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
                    "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence",
                    "tib_softcap_f32", "tib_short_conv", "tib_ssd_scan", "tib_ssd_scan_max_state", "tib_ssd_scan_run", "tib_gated_group_norm",
-                   "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention"):
+                   "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention", "tib_hyper_step"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -169,13 +169,20 @@ def add_rmsnorm(delta: torch.Tensor | None, residual: torch.Tensor, weight: torc
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
-    """RMSNorm over the last dimension of rows held in the activation type."""
-    _need(x, "x"), _need(weight, "weight", torch.float32), _need(out, "out", x.dtype)
+    """RMSNorm over the last dimension of rows held in the activation type (``x`` may be a column slice of wider
+    2-D rows; ``out`` is contiguous)."""
+    _need(weight, "weight", torch.float32), _need(out, "out", x.dtype)
     hidden = x.shape[-1]
+    if x.dim() == 2 and not x.is_contiguous():
+        _rows_of(x, "x")
+        ldx = x.stride(0)
+    else:
+        _need(x, "x")
+        ldx = hidden
     n_rows = x.numel() // hidden if hidden else 0
     if out.shape != x.shape or weight.numel() != hidden:
         raise KernelError("rmsnorm: shapes do not fit")
-    _check("rmsnorm", lib().tib_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), c_int(n_rows), c_int(hidden),
+    _check("rmsnorm", lib().tib_rmsnorm(_ptr(x), c_int64(ldx), _ptr(weight), _ptr(out), c_int(n_rows), c_int(hidden),
                                         c_float(eps), c_int(_code(x.dtype)), _stream()))
     return out
 
@@ -749,11 +756,14 @@ def unit_norm_add(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor,
 
 
 def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, weight: torch.Tensor | None = None,
-                 eps: float = 0.0) -> torch.Tensor:
-    """out = f(x) * sigmoid(gate) row by row; f is the RMS norm with ``weight`` when one is given, else the identity."""
+                 eps: float = 0.0, group: int = 1) -> torch.Tensor:
+    """out = f(x) * sigmoid(gate) row by row; f is the RMS norm with ``weight`` when one is given, else the identity.
+    ``group`` > 1: one gate per run of ``group`` columns (a head), ``gate`` then has width / group columns."""
     _need(out, "out")
     n, width = out.shape
-    _rows_of(x, "x", width), _rows_of(gate, "gate", width)
+    if group < 1 or width % group:
+        raise KernelError("sigmoid_gate: the group does not divide the width")
+    _rows_of(x, "x", width), _rows_of(gate, "gate", width // group)
     if weight is not None:
         _need(weight, "weight", torch.float32)
         if weight.numel() != width:
@@ -762,7 +772,7 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, weight:
         raise KernelError("sigmoid_gate: row counts differ")
     _check("sigmoid_gate", lib().tib_sigmoid_gate(
         _ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(gate), c_int(_code(gate.dtype)), c_int64(gate.stride(0)),
-        _ptr(weight), c_float(eps), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+        _ptr(weight), c_float(eps), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), c_int(group), _stream()))
     return out
 
 
@@ -868,9 +878,10 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: tor
 def latent_append(dkv: torch.Tensor, q: torch.Tensor, folded: torch.Tensor, keys: torch.Tensor | None,
                   positions: torch.Tensor, token_slot: torch.Tensor | None, block_table: torch.Tensor | None,
                   norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, heads: int, dim: int, rank: int, rot: int,
-                  error_word: torch.Tensor | None = None) -> None:
+                  error_word: torch.Tensor | None = None, half_pairs: bool = False) -> None:
     """Norm the latent, rotate the shared key part and store both in the tokens' pages (``keys``: [pages, 1, page_size,
-    rank + rot], or None to store nothing); rotate every head's query part into ``folded[..., rank:]``."""
+    rank + rot], or None to store nothing); rotate every head's query part into ``folded[..., rank:]``.  The rotary pairs
+    are (2i, 2i + 1), or with ``half_pairs`` (i, i + len(inv_freq)), over the first 2 * len(inv_freq) rotated elements."""
     _rows_of(dkv, "dkv", rank + rot), _rows_of(q, "q", heads * (dim + rot))
     _need(folded, "folded", torch.float32), _need(positions, "positions", torch.int32)
     _need(norm_weight, "norm_weight", torch.float32), _need(inv_freq, "inv_freq", torch.float32)
@@ -890,7 +901,7 @@ def latent_append(dkv: torch.Tensor, q: torch.Tensor, folded: torch.Tensor, keys
         _ptr(dkv), c_int64(dkv.stride(0)), _ptr(q), c_int64(q.stride(0)), _ptr(keys), _ptr(folded), _ptr(positions),
         _ptr(token_slot), _ptr(block_table), c_int(table_stride), _ptr(norm_weight), c_float(eps), _ptr(inv_freq),
         c_int(inv_freq.numel()), c_int(n), c_int(heads), c_int(dim), c_int(rank), c_int(rot), c_int(page_size),
-        c_int64(page_stride), c_int(num_pages), _ptr(error_word), c_int(_code(dkv.dtype)), _stream()))
+        c_int64(page_stride), c_int(num_pages), c_int(int(half_pairs)), _ptr(error_word), c_int(_code(dkv.dtype)), _stream()))
 
 
 def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor, kv_start: torch.Tensor,
@@ -927,7 +938,8 @@ def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor
 
 
 # ---------------------------------------------------------------------------
-MOE_ACT = {"none": 0, "relu2": 1, "silu": 2, "glu_clamp": 3}
+MOE_ACT = {"none": 0, "relu2": 1, "silu": 2, "glu_clamp": 3, "swiglu": 4}
+MOE_GATED = ("glu_clamp", "swiglu")      # activations over (gate, up) row pairs: half as many columns leave
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -942,18 +954,27 @@ def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, weights: torch.Tensor, *,
-              sigmoid_scores: bool = False, normalize: bool = True, norm_eps: float = 0.0) -> None:
+              sigmoid_scores: bool = False, normalize: bool = True, norm_eps: float = 0.0,
+              correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1) -> None:
     """From fp32 router logits (the first ``experts`` columns of ``logits``): the ``top`` best experts of every token and
-    their weights."""
+    their weights.  ``correction`` [experts] is added to the scores for the choice only (the weights are made from the
+    scores themselves); with ``groups`` > 1 the experts form that many equal runs of neighbours, and only those of the
+    ``keep`` runs whose best choice score is largest can be chosen."""
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1 or logits.shape[1] < experts:
         raise KernelError("moe_route: logits must be 2-D fp32 with unit inner stride and at least `experts` columns")
     _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32)
     n = logits.shape[0]
     if ids.shape != (n, top) or weights.shape != (n, top):
         raise KernelError("moe_route: ids / weights must be [tokens, top]")
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        if correction.numel() != experts:
+            raise KernelError("moe_route: correction must hold one number per expert")
+    if groups <= 1:
+        groups = keep = 1
     _check("moe_route", lib().tib_moe_route(_ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(experts), c_int(top),
-                                            c_int(int(sigmoid_scores)), c_int(int(normalize)), c_float(norm_eps), _ptr(ids),
-                                            _ptr(weights), _stream()))
+                                            c_int(int(sigmoid_scores)), c_int(int(normalize)), c_float(norm_eps),
+                                            _ptr(correction), c_int(groups), c_int(keep), _ptr(ids), _ptr(weights), _stream()))
 
 
 def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
@@ -972,11 +993,12 @@ def moe_expert_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, offset
     """y[s] = act(row_scale[pair of s] * (x[source of s] . w[expert of s]^T)) for the sorted rows s; ``w``: [experts, N, K];
     ``x_by_pair``: the source of sorted row s is token order[s] // top, else row s itself.  ``act="glu_clamp"``: the rows
     of ``w`` are (gate i, up i) pairs and y has N / 2 columns: g * sigmoid(alpha g) * (u + 1) with g = min(g, limit),
-    u = clamp(u, -limit, limit).  ``row_scale``: one fp32 factor per (token, choice) pair, or None."""
+    u = clamp(u, -limit, limit); ``act="swiglu"``: silu(g) * u over the same pairs.  ``row_scale``: one fp32 factor per
+    (token, choice) pair, or None."""
     _rows_of(x, "x"), _need(w, "w"), _rows_of(y, "y")
     experts, n, k = w.shape
     pairs = order.numel()
-    if x.shape[1] != k or y.shape != (pairs, n // 2 if act == "glu_clamp" else n) or offsets.numel() != experts + 1:
+    if x.shape[1] != k or y.shape != (pairs, n // 2 if act in MOE_GATED else n) or offsets.numel() != experts + 1:
         raise KernelError("moe_expert_product: shapes do not fit")
     if row_scale is not None:
         _need(row_scale, "row_scale", torch.float32)
@@ -990,9 +1012,12 @@ def moe_expert_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, offset
 
 
 def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor,
-                shared: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+                shared: torch.Tensor | None = None, gate: torch.Tensor | None = None, *, ids: torch.Tensor | None = None,
+                identity_from: int = 0, x: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = sum_k weights[t, k] * y[place[t, k]] (+ sigmoid(gate[t]) * shared[t]); ``gate``: one fp32 logit per token
-    (a column view is fine); ``weights`` None: every weight is 1 (``place`` then is [tokens, top])."""
+    (a column view is fine); ``weights`` None: every weight is 1 (``place`` then is [tokens, top]).  With ``ids`` [tokens,
+    top], a choice whose id is ``identity_from`` or above stands for no expert: it adds weights[t, k] * x[t], the experts'
+    input rows ``x`` (of ``out``'s type)."""
     _need(y, "y", torch.float32), _need(place, "place", torch.int32), _need(out, "out")
     n, width = out.shape
     if weights is not None:
@@ -1011,9 +1036,19 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor | No
         if gate.dtype != torch.float32 or gate.shape[0] != n:
             raise KernelError("moe_combine: gate must hold one fp32 logit per token")
         ld_gate = gate.stride(0)
+    ldx = 0
+    if ids is not None:
+        _need(ids, "ids", torch.int32)
+        if x is None or ids.numel() != n * top:
+            raise KernelError("moe_combine: choices that hand the input through need ids [tokens, top] and the input rows")
+        _rows_of(x, "x", width)
+        if x.dtype != out.dtype or x.shape[0] != n:
+            raise KernelError("moe_combine: the input rows must have the output's type and row count")
+        ldx = x.stride(0)
     _check("moe_combine", lib().tib_moe_combine(
         _ptr(y), _ptr(place), _ptr(weights), c_int(top), _ptr(shared), c_int(_code(shared.dtype) if shared is not None else 0),
-        _ptr(gate), c_int64(ld_gate), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+        _ptr(gate), c_int64(ld_gate), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _ptr(ids),
+        c_int(identity_from), _ptr(x if ids is not None else None), c_int64(ldx), _stream()))
     return out
 
 
@@ -1086,10 +1121,14 @@ def layernorm_tail(residual: torch.Tensor, eps: float, *, y: torch.Tensor | None
 def qk_norm_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, keys: torch.Tensor | None,
                    values: torch.Tensor | None, positions: torch.Tensor, token_slot: torch.Tensor | None,
                    block_table: torch.Tensor | None, inv_freq: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
-                   *, rot_dim: int, interleaved: bool = False, eps: float = -1.0, error_word: torch.Tensor | None = None) -> torch.Tensor:
+                   *, rot_dim: int, interleaved: bool = False, eps: float = -1.0, error_word: torch.Tensor | None = None,
+                   q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None, temp_coef: float = 0.0,
+                   temp_every: int = 0) -> torch.Tensor:
     """Rotate part of every q and k head of the fused projection ``proj`` (columns q_off.., k_off.., v_off..), divide each
     head by its root mean square (``eps`` < 0: not), write q to ``q_out`` and k, v into their pages (``keys`` /
-    ``values``: [pages, kv_heads, page_size, dim / vdim] views of one layer's pages).  ``keys`` None: only q."""
+    ``values``: [pages, kv_heads, page_size, dim / vdim] views of one layer's pages).  ``keys`` None: only q.
+    ``q_weight`` / ``k_weight`` [dim] multiply every normed q / k head; ``temp_every`` > 0 multiplies every q by
+    1 + temp_coef * ln(floor((position + 1) / temp_every) + 1).  ``inv_freq`` may be None when ``rot_dim`` is 0."""
     _rows_of(proj, "proj"), _need(q_out, "q_out", proj.dtype), _need(positions, "positions", torch.int32)
     n = proj.shape[0]
     if q_out.shape != (n, heads * dim):
@@ -1104,12 +1143,15 @@ def qk_norm_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out
             raise KernelError("qk_norm_append: keys / values are not one layer's pages")
         _need(token_slot, "token_slot", torch.int32), _need(block_table, "block_table", torch.int32)
         num_pages, page_size, page_stride, table_stride = keys.shape[0], keys.shape[2], keys.stride(0), block_table.stride(0)
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != dim or not t.is_contiguous() or not t.is_cuda):
+            raise KernelError(f"qk_norm_append: {name} must be {dim} fp32 numbers")
     _check("qk_norm_append", lib().tib_qk_norm_append(
         _ptr(proj), c_int64(proj.stride(0)), c_int(q_off), c_int(k_off if write else -1), c_int(v_off), _ptr(q_out),
         _ptr(keys), _ptr(values), _ptr(positions), _ptr(token_slot if write else None), _ptr(block_table if write else None),
         c_int(table_stride), _ptr(inv_freq), c_int(n), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(rot_dim),
-        c_int(int(interleaved)), c_float(eps), c_int(page_size), c_int64(page_stride), c_int(num_pages), _ptr(error_word),
-        c_int(_code(proj.dtype)), _stream()))
+        c_int(int(interleaved)), c_float(eps), c_int(page_size), c_int64(page_stride), c_int(num_pages), _ptr(q_weight),
+        _ptr(k_weight), c_float(temp_coef), c_int(temp_every), _ptr(error_word), c_int(_code(proj.dtype)), _stream()))
     return q_out
 
 
@@ -1344,11 +1386,14 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
                             max_q_len: int, heads: int, kv_heads: int, *, window: int, pool: int, scale: float,
                             temp: torch.Tensor | None = None, sink: torch.Tensor | None = None,
                             value_freq: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                            error_word: torch.Tensor | None = None, force_simt: bool = False) -> torch.Tensor:
+                            error_word: torch.Tensor | None = None, force_simt: bool = False,
+                            rel_bias: torch.Tensor | None = None) -> torch.Tensor:
     """Per head, out[i] = sigmoid(gate[i]) * turn_back_i(sum_j w_ij v_j + sum_b w_ib V_b): softmax weights over the tokens j
     with 0 <= i - j < window and the blocks b of ``pool`` positions with b * pool + pool - 1 <= i - window (their means K_b,
     V_b from the strided pages), scores q . k * scale * temp[h], exp(sink[h]) added to the denominator; turn_back undoes at
     position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone.
+    ``rel_bias`` [heads, span] fp32: rel_bias[h, min(i - j, span - 1)] is added to the score of token j (as it is: neither
+    ``scale`` nor ``temp`` multiplies it).
     bfloat16 steps run on the tensor cores when the head sizes are multiples of 8 up to 128, unless ``force_simt``."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim = keys.shape[3], values.shape[3]
@@ -1371,6 +1416,10 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
     if gate is not None:
         _rows_of(gate, "gate", heads * vdim)
         ld_gate = gate.stride(0)
+    if rel_bias is not None:
+        _need(rel_bias, "rel_bias", torch.float32)
+        if rel_bias.dim() != 2 or rel_bias.shape[0] != heads or rel_bias.shape[1] < 1:
+            raise KernelError("pooled_window_attention: rel_bias must be [heads, span]")
     _check("pooled_window_attention", lib().tib_pooled_window_attention(
         _ptr(q), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(keys), _ptr(values), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), c_int64(page_stride), c_int(num_pages),
@@ -1378,5 +1427,57 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
         _ptr(block_block_table if pool > 0 else None), c_int(b_table_stride), c_int(b_page_size), c_int64(b_stride), c_int(b_pages),
         c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(window), c_int(pool),
         c_float(scale), _ptr(temp), _ptr(sink), _ptr(value_freq), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
-        c_int64(ld_gate), _ptr(error_word), c_int(_code(q.dtype)), c_int(int(force_simt)), _stream()))
+        c_int64(ld_gate), _ptr(rel_bias), c_int(rel_bias.shape[1] if rel_bias is not None else 0), _ptr(error_word),
+        c_int(_code(q.dtype)), c_int(int(force_simt)), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# A residual in several streams, and the tanh norm (csrc/hyper_streams.cu).
+def hyper_step(streams: torch.Tensor, *, y: torch.Tensor | None = None, mix: torch.Tensor | None = None,
+               out_weights: torch.Tensor | None = None, in_weights: torch.Tensor | None = None, out: torch.Tensor | None = None,
+               rows: torch.Tensor | None = None, tanh_norm: tuple[float, torch.Tensor, torch.Tensor] | None = None
+               ) -> torch.Tensor | None:
+    """On streams [S, tokens, width] (fp32), in one launch: with ``y`` the write x_t <- sum_s mix[s, t] x_s + out_weights[t] y
+    (all streams from the old ones), then with ``in_weights`` the read u = sum_s in_weights[s] x_s into ``out``: as fp32
+    sums, or with ``tanh_norm`` = (alpha, weight, bias) as tanh(alpha u) * weight + bias in ``out``'s type.  With ``rows``
+    (int32 token rows) only those rows are read, ``out`` has one row per index and nothing is stored."""
+    _need(streams, "streams", torch.float32)
+    if streams.dim() != 3:
+        raise KernelError("hyper_step: streams must be [S, tokens, width]")
+    count, n, width = streams.shape
+    if y is not None:
+        _rows_of(y, "y", width)
+        if y.shape[0] != n or mix is None or out_weights is None:
+            raise KernelError("hyper_step: a write needs y [tokens, width], mix and out_weights")
+        _need(mix, "mix", torch.float32), _need(out_weights, "out_weights", torch.float32)
+        if mix.shape != (count, count) or out_weights.numel() != count:
+            raise KernelError("hyper_step: mix must be [S, S] and out_weights [S]")
+    n_out = n
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    norm, alpha, weight, bias = 0, 0.0, None, None
+    if in_weights is not None:
+        _need(in_weights, "in_weights", torch.float32)
+        if out is None or in_weights.numel() != count:
+            raise KernelError("hyper_step: a read needs in_weights [S] and out")
+        _need(out, "out")
+        if out.shape != (n_out, width):
+            raise KernelError(f"hyper_step: out is {tuple(out.shape)}, wanted {(n_out, width)}")
+        if tanh_norm is not None:
+            alpha, weight, bias = tanh_norm
+            _need(weight, "weight", torch.float32), _need(bias, "bias", torch.float32)
+            if weight.numel() != width or bias.numel() != width:
+                raise KernelError("hyper_step: the norm's weight and bias do not fit the width")
+            norm = 1
+        elif out.dtype != torch.float32:
+            raise KernelError("hyper_step: sums without a norm leave in fp32")
+    elif rows is not None:
+        raise KernelError("hyper_step: rows only make sense with a read")
+    _check("hyper_step", lib().tib_hyper_step(
+        _ptr(streams), c_int64(streams.stride(0)), c_int(count), c_int(n_out), c_int(width), _ptr(y),
+        c_int(_code(y.dtype) if y is not None else 0), c_int64(y.stride(0) if y is not None else 0), _ptr(mix),
+        _ptr(out_weights), _ptr(in_weights), _ptr(rows), c_int(norm), c_float(alpha), _ptr(weight), _ptr(bias), _ptr(out),
+        c_int(_code(out.dtype) if out is not None else 0), _stream()))
     return out

@@ -56,7 +56,7 @@ class CausalLM:
         for prefix, part in self._owned_parts():
             for ws in part.weight_specs():
                 name = prefix + ws.name
-                expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
+                expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional, ws.free_dims)
             for ws in part.shared_weight_specs():
                 if ws.name in expected and tuple(expected[ws.name].shape) != tuple(ws.shape):
                     raise ValueError(f"{ws.name}: parts that share it declare shapes {expected[ws.name].shape} and {ws.shape}")
@@ -168,6 +168,8 @@ class CausalLM:
             residual = history[1]
         stream = ResidualStream(residual, self.dtype)
         stream.history = history
+        if self.spec.streams:
+            stream.streams = residual.unsqueeze(0).repeat(self.spec.streams, 1, 1)      # every stream starts as the embedding output
         if self.spec.keeps_embedding_output:
             stream.origin = residual.clone()
         if self.after_embedding is not None:

@@ -59,8 +59,13 @@ class ModelSpec:
     history_depth: int = 0                    # > 0: the residual stream lives in a [depth, tokens, hidden] tensor whose
                                               # slice 0 keeps the embedding output and whose later slices keep what
                                               # blocks leave there (``ResidualStream.history``); the stream starts in slice 1
+    streams: int = 0                          # > 0: the residual is carried in this many streams [streams, tokens, hidden]
+                                              # (``ResidualStream.streams``), each the embedding output at the start; blocks
+                                              # of kind ``hyper_connection`` read and write them; the output is their sum
 
     def __post_init__(self) -> None:
+        if self.streams and self.history_depth:
+            raise ValueError("a residual in several streams and a history of layer outputs do not go together")
         for call in self.schedule:
             if isinstance(call, StageCall):
                 if not 0 <= call.stage < len(self.stages):

@@ -41,11 +41,14 @@ class WeightSpec:
     """One tensor a part reads from the checkpoint, by name relative to its prefix."""
     name: str
     shape: tuple[int, ...]
-    init: str = "normal"       # random mode: "normal" (std), "about_one" (1 + normal), "ones", "zeros"
+    init: str = "normal"       # random mode: "normal" (std), "about_one" (1 + normal), "about_identity" (unit matrix + normal),
+                               # "ones", "zeros"
     std: float = 0.02
     role: str = "matrix"       # "matrix": kept as stored (bf16 / fp32); "vector": widened to fp32;
                                # "int_table": integer table kept as int32
     optional: bool = False     # may be absent from the file (then the part copes)
+    free_dims: tuple[int, ...] = ()   # dimensions whose size the file decides (``shape`` holds what random weights get);
+                                      # the part reads the size off the tensor it is bound to
 
 
 @dataclass(frozen=True)
@@ -127,8 +130,59 @@ class ResidualStream:
         # the residual rows in the activation type, left by whoever last changed the residual and had them at
         # hand; whoever changes the residual next drops it
         self.activation_copy: torch.Tensor | None = None
+        # [S, tokens, hidden] fp32 when the model carries its residual in S streams (ModelSpec.streams): every stream
+        # starts as the embedding output, blocks read them through a weighted sum (:meth:`read_streams`) and write a
+        # sublayer's output back through a matrix (:meth:`write_streams`); the model's output is their sum.
+        # ``residual`` is then not used.
+        self.streams: torch.Tensor | None = None
+        self.pending_write: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None     # (y, mix, out weights)
+        self._unit_weights: torch.Tensor | None = None
+
+    # ------------------------------------------------------- several streams
+    def write_streams(self, y: torch.Tensor, mix: torch.Tensor, out_weights: torch.Tensor) -> None:
+        """x_t <- sum_s mix[s, t] x_s + out_weights[t] * y for all streams at once; left pending so that the next read
+        does it in its own pass."""
+        if self.pending_write is not None:
+            self.settle_streams()
+        self.pending_write = (y, mix, out_weights)
+
+    def settle_streams(self) -> torch.Tensor:
+        if self.pending_write is not None:
+            from torchinferno_b200.kernels import ops
+            y, mix, out_weights = self.pending_write
+            ops.hyper_step(self.streams, y=y, mix=mix, out_weights=out_weights)
+            self.pending_write = None
+        return self.streams
+
+    def read_streams(self, in_weights: torch.Tensor | None, norm: "Norm", rows: torch.Tensor | None = None) -> torch.Tensor:
+        """norm(sum_s in_weights[s] x_s) in the activation type (``in_weights`` None: the plain sum).  A pending write is
+        done on the way (with ``rows`` it is only looked through and stays pending).  A norm that needs no statistic of
+        the row (``tanh_params``) is computed in the same launch; any other gets the sums in fp32."""
+        from torchinferno_b200.kernels import ops
+        streams = self.streams
+        count, n, width = streams.shape
+        if in_weights is None:
+            if self._unit_weights is None:
+                self._unit_weights = torch.ones(count, dtype=torch.float32, device=streams.device)
+            in_weights = self._unit_weights
+        y, mix, out_weights = self.pending_write if self.pending_write is not None else (None, None, None)
+        n_out = n if rows is None else rows.numel()
+        out = torch.empty((n_out, width), dtype=self.dtype, device=streams.device)
+        params = getattr(norm, "tanh_params", None)
+        if params is not None:
+            ops.hyper_step(streams, y=y, mix=mix, out_weights=out_weights, in_weights=in_weights, out=out, rows=rows,
+                           tanh_norm=params())
+        else:
+            sums = torch.empty((n_out, width), dtype=torch.float32, device=streams.device)
+            ops.hyper_step(streams, y=y, mix=mix, out_weights=out_weights, in_weights=in_weights, out=sums, rows=rows)
+            norm.forward(sums, out)
+        if rows is None:
+            self.pending_write = None
+        return out
 
     def normed(self, norm: "Norm", rows: torch.Tensor | None = None) -> torch.Tensor:
+        if self.streams is not None:
+            return self.read_streams(None, norm, rows)
         n = self.residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.residual.shape[1]), dtype=self.dtype, device=self.residual.device)
         if self.pending is None:
@@ -272,6 +326,7 @@ def _ensure_builtin() -> None:
     if _loaded:
         return
     _loaded = True
-    from torchinferno_b200.parts import (attention, block, gated_recurrence, latent_attention, linear_attention, mlp,  # noqa: F401
-                                         moe, norm, parallel_block, pooled_window_attention, rope, sandwich_block,
-                                         sigmoid_attention, state_space, stream_stages)
+    from torchinferno_b200.parts import (attention, biased_attention, block, gated_recurrence, hyper_block,  # noqa: F401
+                                         latent_attention, linear_attention, mlp, moe, norm, parallel_block,
+                                         pooled_window_attention, rope, sandwich_block, sigmoid_attention, state_space,
+                                         stream_stages)

@@ -12,6 +12,15 @@ as one product over row pairs (gate i, up i).  ``weight_on_input``: the router w
 instead of its output, sum of expert(w x); it is applied to the 32-bit sums of the first product, ahead of the clamps
 (W (w x) = w (W x)), so the input rows are not rounded a second time.
 
+``activation="swiglu"``: an expert is the plain gated unit W_down (silu(W_gate x) * (W_up x)), gate and up again as row
+pairs of one product.
+
+``identity`` = n > 0: the router has ``experts`` + n outputs, and the last n stand for experts without tensors whose
+output is their input (times the weight).  ``correction``: a tensor of one number per router output that is added to the
+scores for the choice only; the weights are made from the scores themselves.  ``groups`` = (count, keep): the router's
+outputs (identity ones included) form ``count`` equal groups of neighbours, a group's score is its largest choice score,
+and only members of the best ``keep`` groups can be chosen.
+
 The pairs (token, choice) are sorted by expert on the device and both products run over the sorted rows
 (csrc/moe.cu); no count comes back to the host, so a step with this part may be captured.
 """
@@ -32,20 +41,32 @@ class RoutedExperts(FeedForward):
                  shared_gate: bool = False, router_name: str = "router", expert_prefix: str = "e", up_name: str = "up",
                  down_name: str = "down", shared_prefix: str = "shared.", shared_gate_name: str = "sg", gate_name: str = "gate",
                  limit: float = 0.0, shared_limit: float | None = None, alpha: float = 1.702, weight_on_input: bool = False,
-                 dtype: torch.dtype, device: torch.device) -> None:
+                 identity: int = 0, correction: bool = False, correction_name: str = "correction",
+                 groups: tuple[int, int] | None = None, dtype: torch.dtype, device: torch.device) -> None:
         super().__init__(dtype=dtype, device=device)
-        if not 1 <= top <= experts:
-            raise ValueError("top must be between 1 and the number of experts")
-        if activation not in ("relu2", "silu", "glu_clamp") or scores not in ("softmax", "sigmoid"):
+        self.identity = int(identity)
+        self.routed = experts + self.identity          # outputs of the router
+        if experts < 1 or self.identity < 0 or not 1 <= top <= self.routed:
+            raise ValueError("top must be between 1 and the number of experts (identity ones included)")
+        if activation not in ("relu2", "silu", "glu_clamp", "swiglu") or scores not in ("softmax", "sigmoid"):
             raise ValueError(f"unknown activation {activation!r} or scores {scores!r}")
+        self.groups = None if groups is None else (int(groups[0]), int(groups[1]))
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or not 1 <= keep <= count or self.routed % count or top > keep * (self.routed // count):
+                raise ValueError("groups: equal groups, of which at least one and at most all are kept, with room for `top` choices")
+        if self.identity and weight_on_input:
+            raise ValueError("experts that hand their input through take their weight on the output")
+        self.has_correction, self.correction_name = bool(correction), correction_name
+        self.correction: torch.Tensor | None = None
         self.hidden_size, self.experts, self.top, self.expert_size = hidden_size, experts, top, expert_size
         self.activation, self.scores, self.normalize, self.norm_eps = activation, scores, bool(normalize), float(norm_eps)
         self.shared_size, self.shared_gate = int(shared_size or 0), bool(shared_gate and shared_size)
         self.names = (router_name, expert_prefix, up_name, down_name, shared_prefix, shared_gate_name)
-        self.gate_name, self.glu = gate_name, activation == "glu_clamp"
+        self.gate_name, self.glu = gate_name, activation in ("glu_clamp", "swiglu")       # (gate and up as row pairs)
         self.limit, self.alpha, self.weight_on_input = float(limit), float(alpha), bool(weight_on_input)
         self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
-        if self.glu and not self.limit > 0:
+        if activation == "glu_clamp" and not self.limit > 0:
             raise ValueError("the clamped gated unit needs a positive limit")
 
     def _expert(self, e: int, which: str) -> str:
@@ -55,7 +76,9 @@ class RoutedExperts(FeedForward):
     def weight_specs(self) -> list[WeightSpec]:
         router, _, up, down, shared, gate = self.names
         std = self.hidden_size ** -0.5          # (random weights: rows of about unit size from normed input)
-        specs = [WeightSpec(router, (self.experts, self.hidden_size), std=2 * std)]
+        specs = [WeightSpec(router, (self.routed, self.hidden_size), std=2 * std)]
+        if self.has_correction:
+            specs.append(WeightSpec(self.correction_name, (self.routed,), std=0.05, role="vector"))
         for e in range(self.experts):
             if self.glu:
                 specs.append(WeightSpec(self._expert(e, "gate"), (self.expert_size, self.hidden_size), std=std))
@@ -74,6 +97,8 @@ class RoutedExperts(FeedForward):
         router, _, up, down, shared, gate = self.names
         rows = [weights[router]] + ([weights[shared + gate]] if self.shared_gate else [])
         self.router_weight = torch.cat(rows, dim=0).to(torch.float32).contiguous()      # (the router is fp32 in both modes)
+        if self.has_correction:
+            self.correction = weights[self.correction_name].to(torch.float32).contiguous()
         def first(name_of) -> torch.Tensor:
             """The first product's matrix: up, or (gate i, up i) row pairs for the gated unit."""
             if not self.glu:
@@ -94,8 +119,9 @@ class RoutedExperts(FeedForward):
         ops.router_logits(x, self.router_weight, logits)
         ids = torch.empty((n, top), dtype=torch.int32, device=dev)
         weights = torch.empty((n, top), dtype=torch.float32, device=dev)
-        ops.moe_route(logits, self.experts, top, ids, weights, sigmoid_scores=self.scores == "sigmoid",
-                      normalize=self.normalize, norm_eps=self.norm_eps)
+        count, keep = self.groups if self.groups is not None else (1, 1)
+        ops.moe_route(logits, self.routed, top, ids, weights, sigmoid_scores=self.scores == "sigmoid",
+                      normalize=self.normalize, norm_eps=self.norm_eps, correction=self.correction, groups=count, keep=keep)
         offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
         order = torch.empty(n * top, dtype=torch.int32, device=dev)
         place = torch.empty(n * top, dtype=torch.int32, device=dev)
@@ -110,16 +136,18 @@ class RoutedExperts(FeedForward):
             hidden = linear(x, self.shared_up_weight)
             if self.activation == "relu2":
                 ops.relu_squared(hidden, hidden)
-            elif self.glu:
+            elif self.activation == "glu_clamp":
                 hidden = ops.glu_clamp(hidden, torch.empty((n, self.shared_size), dtype=hidden.dtype, device=dev),
                                        self.shared_limit, self.alpha)
             else:
                 raise NotImplementedError("a shared expert with silu")
             shared_rows = linear(hidden, self.shared_down_weight)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=dev)
-        gate = logits[:, self.experts] if self.shared_gate else None
+        gate = logits[:, self.routed] if self.shared_gate else None
+        # (a choice at or beyond `experts` found no place among the sorted rows: it adds the input itself)
         return ops.moe_combine(outer, place.view(n, top) if self.weight_on_input else place,
-                               None if self.weight_on_input else weights, out, shared_rows, gate)
+                               None if self.weight_on_input else weights, out, shared_rows, gate,
+                               ids=ids if self.identity else None, identity_from=self.experts, x=x if self.identity else None)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -99,7 +99,8 @@ def load_weights(model, folder: str | Path) -> dict[str, object]:
                 continue
             view = handle_of(files[name]).get_slice(name)
             shape = tuple(view.get_shape())
-            if shape != tuple(ws.shape):
+            free = getattr(ws, "free_dims", ())
+            if len(shape) != len(ws.shape) or any(a != b for d, (a, b) in enumerate(zip(shape, ws.shape)) if d not in free):
                 wrong.append(f"{name}: file {list(shape)} vs model {list(ws.shape)}")
         if missing or unexpected or wrong:
             parts = [f"checkpoint {folder} does not fit the model ({model.spec.architecture}):"]

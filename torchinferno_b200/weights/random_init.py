@@ -1,4 +1,5 @@
-"""Random weights: every matrix N(0, std), norm vectors 1 (or 1 + N(0, std) where a part asks for it), from a seed.
+"""Random weights: every matrix N(0, std), norm vectors 1 (or 1 + N(0, std) where a part asks for it; small square
+matrices of coefficients the unit matrix + N(0, std)), from a seed.
 
 Each tensor has a generator of its own, keyed by (seed, tensor name), so a
 tensor's values do not depend on which other tensors exist or on their order.
@@ -30,7 +31,7 @@ def random_tensor(spec, seed: int, *, device: torch.device | str = "cpu",
         return torch.ones(spec.shape, dtype=dtype, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype, device=device)
-    if spec.init not in ("normal", "about_one"):
+    if spec.init not in ("normal", "about_one", "about_identity"):
         raise ValueError(f"unknown init {spec.init!r} for {spec.name}")
     generator = torch.Generator(device=device)
     generator.manual_seed(_tensor_seed(seed, spec.name))
@@ -38,6 +39,8 @@ def random_tensor(spec, seed: int, *, device: torch.device | str = "cpu",
     out.normal_(0.0, spec.std, generator=generator)
     if spec.init == "about_one":
         out += 1.0
+    if spec.init == "about_identity":          # (a square matrix: the unit matrix plus noise)
+        out += torch.eye(spec.shape[0], spec.shape[1], device=device)
     return out.to(dtype)
 
 
