@@ -125,11 +125,9 @@ def biased_attention(h, w, p, m, positions, eps):
     rel = w[p + "rel"]                                                                            # [buckets, H]
     kh, vh = k.repeat_interleave(H // G, dim=1), v.repeat_interleave(H // G, dim=1)
     scores = torch.einsum("ihd,jhd->hij", q, kh) * m["scale"]
-    pos = positions.tolist()
-    bias = torch.zeros(H, T, T, dtype=F)
-    for i in range(T):
-        for j in range(i + 1):
-            bias[:, i, j] = rel[distance_bucket(pos[i] - pos[j], rel.shape[0], m["bias_max"])]
+    distance = (positions[:, None] - positions[None, :]).clamp(min=0)                             # [T, T]; j > i is masked anyway
+    row_of = torch.tensor([distance_bucket(n, rel.shape[0], m["bias_max"]) for n in range(int(distance.max()) + 1)])
+    bias = rel[row_of[distance]].permute(2, 0, 1)                                                 # [H, T, T]
     heads = torch.einsum("hij,jhd->ihd", causal_softmax(scores + bias), vh)
     return heads.reshape(T, H * dv) @ w[p + "o"].T
 
@@ -139,26 +137,38 @@ def gated_unit(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def route(h, w, p, router):
+def route(h, w, p, router, gaps=None):
     """(ids [T, top], weights [T, top]): softmax scores over experts and identity experts; the choice adds the correction
     and looks only at the best ``keep`` of ``count`` groups of neighbours (a group's score is its largest choice score);
-    the weights are the chosen scores without the correction, divided by their sum + 1e-20."""
+    the weights are the chosen scores without the correction, divided by their sum + 1e-20.  ``gaps`` (a list) receives
+    per token the smallest margin by which a choice was made: between the last group kept and the first one dropped, and
+    between the last output chosen and the first one left."""
     n = router["experts"] + router["identity"]
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)
     choice = s + w[p + "correction"]
     count, keep = router["groups"]["count"], router["groups"]["keep"]
     group_score = choice.view(-1, count, n // count).max(dim=-1).values
+    ranked = group_score.sort(dim=-1, descending=True)
     kept = torch.zeros_like(group_score, dtype=torch.bool)
-    kept.scatter_(1, group_score.topk(keep, dim=-1).indices, True)
+    kept.scatter_(1, ranked.indices[:, :keep], True)
     choice = choice.masked_fill(~kept.repeat_interleave(n // count, dim=1), -math.inf)
-    ids = choice.topk(router["top"], dim=-1).indices
+    order = choice.sort(dim=-1, descending=True)
+    ids = order.indices[:, :router["top"]]
+    if gaps is not None:
+        for t in range(h.shape[0]):
+            margin = math.inf
+            if keep < count:
+                margin = float(ranked.values[t, keep - 1] - ranked.values[t, keep])
+            if router["top"] < n and order.values[t, router["top"]] > -math.inf:
+                margin = min(margin, float(order.values[t, router["top"] - 1] - order.values[t, router["top"]]))
+            gaps.append(margin)
     chosen = s.gather(1, ids)
     return ids, chosen / (chosen.sum(dim=-1, keepdim=True) + 1e-20)
 
 
-def routed_units(h, w, p, mlp):
+def routed_units(h, w, p, mlp, gaps=None):
     router = mlp["router"]
-    ids, weights = route(h, w, p, router)
+    ids, weights = route(h, w, p, router, gaps)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t].tolist(), weights[t]):
@@ -167,8 +177,9 @@ def routed_units(h, w, p, mlp):
 
 
 # -------------------------------------------------------------------- model
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence from its first token (and the sum of the streams after every layer)."""
+def forward(config, w, tokens, return_layers=False, gaps=None):
+    """Logits [T, vocab] of one sequence from its first token (and the sum of the streams after every layer).  ``gaps`` (a
+    list of one list per token) receives the margins of every router's choice for that token."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.numel())
     eps, S = config["norm"]["eps"], config["streams"]
@@ -181,7 +192,10 @@ def forward(config, w, tokens, return_layers=False):
         x = write_streams(x, w[p + "hc1.mix"], w[p + "hc1.out"], mixer(u, w, p + "mix.", layer["mixer"], positions, eps))
         if layer["mlp"] is not None:
             u = tanh_norm(read_streams(x, w[p + "hc2.in"]), w, p + "norm2")
-            y = gated_unit(u, w, p + "mlp.") if layer["mlp"]["kind"] == "dense" else routed_units(u, w, p + "mlp.", layer["mlp"])
+            margins = [] if gaps is not None else None
+            y = gated_unit(u, w, p + "mlp.") if layer["mlp"]["kind"] == "dense" else routed_units(u, w, p + "mlp.", layer["mlp"], margins)
+            for t, margin in enumerate(margins or []):
+                gaps[t].append(margin)
             x = write_streams(x, w[p + "hc2.mix"], w[p + "hc2.out"], y)
         after.append(x.sum(dim=0))
     logits = tanh_norm(x.sum(dim=0), w, "final.norm") @ w["head"].T
