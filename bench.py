@@ -467,7 +467,24 @@ def _design_configs(DESIGN_WIDTH: int, DESIGN_HEADS: int, kv_heads: int, dense_f
                            {"type": "mamba2", "mixer": ssd, "mlp": None},
                            {"type": "mamba2", "mixer": ssd, "mlp": dense},
                            {"type": "attention", "mixer": windowed, "mlp": dense}]}
-    return {"zipedra": zipedra, "giforax": giforax, "tibalorn": tibalorn, "llama": llama}
+    # Vofidra beside Zipedra (the closest: attention over the same latent, routed experts of the same sizes) and the same
+    # Llama: a residual in two streams, queries through a latent of 768, grouped attention of the same head counts with a
+    # bias table of 32 rows up to distance 1024, 28 experts and 4 outputs without tensors in four groups of which two are kept
+    latent_q = dict(latent, q_rank=768)
+    biased = {"heads": DESIGN_HEADS, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 1024, "buckets": 32,
+              "q_temp": {"coef": 0.1, "every": 512}}
+    grouped = {"kind": "moe", "expert": {"ff": expert_ff},
+               "router": {"experts": 28, "identity": 4, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    vofidra = {"architecture": "Vofidra", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "streams": 2, "norm": {"eps": 1e-6},
+               "logit_softcap": 30.0,
+               "layers": [{"type": "latent_attention", "mixer": latent_q, "mlp": dense},
+                          {"type": "attention", "mixer": biased, "mlp": grouped},
+                          {"type": "latent_attention", "mixer": latent_q, "mlp": grouped},
+                          {"type": "attention", "mixer": biased, "mlp": dense}]}
+    return {"zipedra": zipedra, "giforax": giforax, "tibalorn": tibalorn, "vofidra": vofidra, "llama": llama}
+
+
+DESIGN_ALSO_BESIDE = {"vofidra": ("zipedra",)}      # the closest design of the package, measured in the same call
 
 
 def run_design(args) -> dict:
@@ -485,7 +502,7 @@ def run_design(args) -> dict:
     points = {}
     with torch.inference_mode():
         for name, config in design_configs(args.design_width).items():
-            if name not in (args.design, "llama"):
+            if name not in (args.design, "llama", *DESIGN_ALSO_BESIDE.get(args.design, ())):
                 continue
             model = random_model(config, seed=0, dtype="bfloat16")
             runner = make_runner(model, page_size=PAGE_SIZE, max_tokens=(batch + 1) * (prompt_len + 256), max_requests=batch + 1,
@@ -528,13 +545,17 @@ def run_design(args) -> dict:
                    "giforax": (["sigmoid-attention"], ["sigmoid-attention", "--chunk", "2048"], ["gated-recurrence"], ["layer-tails"],
                                ["expert-product"]),
                    "tibalorn": (["pooled-window-attention"], ["state-space", "--heads", str(args.design_width // 32)],
-                                ["sigmoid-attention"], ["gated-recurrence"], ["layer-tails"])}[args.design]
+                                ["sigmoid-attention"], ["gated-recurrence"], ["layer-tails"]),
+                   "vofidra": (["biased-attention", "--heads", str(args.design_width // 128), "--kv-heads", str(args.design_width // 256)],
+                               ["latent-attention", "--heads", str(args.design_width // 128)],
+                               ["hyper-streams", "--hidden", str(args.design_width)],
+                               ["expert-product", "--hidden", str(args.design_width), "--expert-size", str(args.design_width // 2)])}[args.design]
             alone = () if args.design_no_kernels else (*own, ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
                                                        ["decode-attention", "--heads", "16", "--kv-heads", "8"])
             for argv in alone:
                 bench_kernels.main(argv)
     kernels = [json.loads(line) for line in lines.getvalue().splitlines() if line.startswith("{")]
-    return {"design": args.design, "beside": "llama", "dtype": "bf16", "data": "synthetic token ids, random weights",
+    return {"design": args.design, "beside": ", ".join((*DESIGN_ALSO_BESIDE.get(args.design, ()), "llama")), "dtype": "bf16", "data": "synthetic token ids, random weights",
             "config": {"width": args.design_width, "heads": args.design_width // 128, "layer_runs": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
                        "prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "page_size": PAGE_SIZE},
             "points": points, "kernels": kernels}
@@ -636,7 +657,7 @@ def main(argv=None) -> int:
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     parser.add_argument("--workloads", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS),
                         help="serving workloads of the smaller sizes to add to points")
-    parser.add_argument("--design", choices=["zipedra", "giforax", "tibalorn"], default=None,
+    parser.add_argument("--design", choices=["zipedra", "giforax", "tibalorn", "vofidra"], default=None,
                         help="instead of the headline run: prefill and decode throughput of this design at layer sizes that "
                              "resemble a real model's, beside the closest Llama, and its kernels against the roofline")
     parser.add_argument("--design-width", type=int, default=DESIGN_WIDTH,

@@ -336,6 +336,9 @@ def run_expert_product(args) -> None:
            timer(lambda: ops.moe_expert_product(x, gate_up, inner, offsets, order, top, x_by_pair=True, act="glu_clamp", limit=7.0,
                                                 alpha=1.702, row_scale=scale)),
            flops=2 * flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
+    report("expert_product[gate and up, silu gated unit]",
+           timer(lambda: ops.moe_expert_product(x, gate_up, inner, offsets, order, top, x_by_pair=True, act="swiglu")),
+           flops=2 * flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
     dense = LinearWeight((torch.randn(top * ff, w, device="cuda") * 0.02).to(torch.bfloat16), few_rows_tcgen05=False)
     report("linear[dense, the same flops]", timer(lambda: linear(x, dense)), flops=flops, tokens=t, hidden=w, out=top * ff)
 
@@ -462,6 +465,72 @@ def run_pooled_window_attention(args) -> None:
     report("rotary_kv_append[prompt]", timer(fn), bytes_moved=n * ((h + k) * d + k * v) * 4, tokens=n)
     fn = lambda: ops.pool_blocks(keys, values, table, bkeys, bvalues, btable, positions, token_slot, pool)
     report("pool_blocks[prompt]", timer(fn), bytes_moved=n * k * (d + v) * 2 + (n // pool) * k * (d + v) * 2, tokens=n, pool=pool)
+
+
+def run_biased_attention(args) -> None:
+    """The causal attention with a learned bias per head and distance on a prompt of --tokens (flops: both products over
+    the keys a query sees) and on --batch single tokens at --context (bytes: the keys and values of every context once);
+    then the launch ahead of it (norm of q and k with a weight, the query's temperature, the store into the pages)."""
+    h, k, d, v, page = args.heads, args.kv_heads, args.head_dim, args.value_dim, args.page_size
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+
+    def pages(n_entries, entries_per):
+        per = -(-entries_per // page)
+        pool_ = (torch.randn(n_entries * per, k * page * (d + v), device="cuda") * 0.5).to(torch.bfloat16)
+        table = torch.randperm(n_entries * per, device="cuda", dtype=torch.int32).view(n_entries, per).contiguous()
+        return pool_[:, :k * page * d].unflatten(1, (k, page, d)), pool_[:, k * page * d:].unflatten(1, (k, page, v)), table
+
+    rel = torch.randn(h, args.bias_max + 1, device="cuda")
+    for mode in ("prompt", "single tokens"):
+        n_entries, ctx = (1, args.tokens) if mode == "prompt" else (args.batch, args.context)
+        keys, values, table = pages(n_entries, ctx)
+        n = ctx if mode == "prompt" else n_entries
+        q = torch.randn(n, h * d, device="cuda").to(torch.bfloat16)
+        out = torch.empty(n, h * v, dtype=torch.bfloat16, device="cuda")
+        if mode == "prompt":
+            q_start, kv_start, slots, max_q = i32([0, n]), i32([0]), i32([0]), n
+            flops, moved = 2 * h * (d + v) * ctx * (ctx + 1) / 2, None
+        else:
+            q_start, kv_start, slots, max_q = i32(list(range(n + 1))), i32([ctx - 1] * n), i32(list(range(n))), 1
+            flops, moved = None, n * ctx * k * (d + v) * 2
+        for name, bias in (("biased_attention", rel), ("the same without the bias", None)):
+            fn = lambda: ops.pooled_window_attention(q, out, q_start, kv_start, slots, keys, values, table, None, None, None, n_entries,
+                                                     max_q, h, k, window=1 << 30, pool=0, scale=0.09, rel_bias=bias)
+            report(f"{name}[{mode}]", timer(fn), flops=flops, bytes_moved=moved, entries=n_entries, context=ctx, heads=h, kv_heads=k,
+                   head_dim=d, value_dim=v, bias_max=args.bias_max)
+    n = args.tokens
+    keys, values, table = pages(1, n)
+    proj = torch.randn(n, (h + k) * d + k * v, device="cuda").to(torch.bfloat16)
+    q = torch.empty(n, h * d, dtype=torch.bfloat16, device="cuda")
+    positions, token_slot = i32(list(range(n))), i32([0] * n)
+    qw, kw = torch.ones(d, device="cuda"), torch.ones(d, device="cuda")
+    fn = lambda: ops.qk_norm_append(proj, 0, h * d, (h + k) * d, q, keys, values, positions, token_slot, table, None, h, k, d, v,
+                                    rot_dim=0, eps=1e-6, q_weight=qw, k_weight=kw, temp_coef=0.1, temp_every=512)
+    report("qk_norm_append[prompt, weights and temperature]", timer(fn), bytes_moved=n * ((h + k) * d + k * v) * 4, tokens=n)
+
+
+def run_hyper_streams(args) -> None:
+    """A residual in --streams streams: the write of a sublayer's output and the read for the next with the tanh norm in one
+    launch (bytes: every stream read and written in fp32, the output rows read, the normed rows written), the read alone,
+    and beside them the residual sum with an RMS norm of a single residual."""
+    rows, w, s = args.rows, args.hidden, args.streams
+    timer = Timer(args.iters)
+    streams = torch.randn(s, rows, w, device="cuda")
+    y = torch.randn(rows, w, device="cuda").to(torch.bfloat16)
+    out = torch.empty(rows, w, dtype=torch.bfloat16, device="cuda")
+    mix = (torch.eye(s, device="cuda") + 0.01).contiguous()
+    coef, wt, b = torch.ones(s, device="cuda") / s, torch.ones(w, device="cuda"), torch.zeros(w, device="cuda")
+    report("hyper_step[write, read, tanh norm]",
+           timer(lambda: ops.hyper_step(streams, y=y, mix=mix, out_weights=coef, in_weights=coef, out=out, tanh_norm=(0.5, wt, b))),
+           bytes_moved=rows * w * (8 * s + 4), rows=rows, hidden=w, streams=s)
+    report("hyper_step[read, tanh norm]", timer(lambda: ops.hyper_step(streams, in_weights=coef, out=out, tanh_norm=(0.5, wt, b))),
+           bytes_moved=rows * w * (4 * s + 2), rows=rows, hidden=w, streams=s)
+    few = min(rows, 8)
+    report("hyper_step[write, read, tanh norm, few rows]",
+           timer(lambda: ops.hyper_step(streams[:, :few], y=y[:few], mix=mix, out_weights=coef, in_weights=coef, out=out[:few],
+                                        tanh_norm=(0.5, wt, b))), bytes_moved=few * w * (8 * s + 4), rows=few, hidden=w, streams=s)
+    report("add_rmsnorm", timer(lambda: ops.add_rmsnorm(y, streams[0], wt, 1e-6, out)), bytes_moved=rows * w * 12, rows=rows, hidden=w)
 
 
 def run_state_space(args) -> None:
@@ -607,6 +676,24 @@ def main(argv=None) -> int:
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--iters", type=int, default=10)
     p.set_defaults(func=run_pooled_window_attention)
+    p = sub.add_parser("biased-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=128)
+    p.add_argument("--bias-max", type=int, default=1024)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_biased_attention)
+    p = sub.add_parser("hyper-streams")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--streams", type=int, default=2)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_hyper_streams)
     p = sub.add_parser("state-space")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--batch", type=int, default=8)
