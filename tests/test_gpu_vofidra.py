@@ -499,6 +499,55 @@ def test_biased_attention_finds_a_far_key_among_many_with_two_requests_side_by_s
     assert (got_other - want_other).abs().max() <= tol * want_other.abs().max()
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(4, 2, 32, 16, 16), (16, 1, 128, 128, 16), (3, 3, 8, 72, 4), (8, 4, 96, 96, 8)])
+def test_single_tokens_whose_contexts_are_shared_out_over_blocks(heads, kv_heads, dim, vdim, page):
+    """A step of single tokens at contexts of 1 to 700 keys, each context's keys shared out over 1, 2, 3 and 7 blocks (and
+    over as many as the step would choose itself): the sums are added to what a single block gives and to what plain
+    arithmetic gives, with the bias table, a sink, and NaN in all unwritten cache."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    g = torch.Generator().manual_seed(heads * 10 + dim)
+    contexts = [700, 1, 65, 64, 333, 129]
+    n = len(contexts)
+    per = -(-max(contexts) // page)
+    keys = torch.full((n * per + 3, kv_heads, page, dim), float("nan"))
+    values = torch.full((n * per + 3, kv_heads, page, vdim), float("nan"))
+    table = torch.randperm(n * per + 3, generator=g)[:n * per].view(n, per).to(torch.int32)
+    k_all = [torch.randn(c, kv_heads, dim, generator=g).to(torch.bfloat16) for c in contexts]
+    v_all = [torch.randn(c, kv_heads, vdim, generator=g).to(torch.bfloat16) for c in contexts]
+    for e, c in enumerate(contexts):
+        for pos in range(c):
+            keys[table[e, pos // page], :, pos % page] = k_all[e][pos].float()
+            values[table[e, pos // page], :, pos % page] = v_all[e][pos].float()
+    pool = torch.cat([keys.flatten(1), values.flatten(1)], dim=1).to(torch.bfloat16).cuda()
+    keys_d = pool[:, :kv_heads * page * dim].unflatten(1, (kv_heads, page, dim))
+    values_d = pool[:, kv_heads * page * dim:].unflatten(1, (kv_heads, page, vdim))
+    q = (torch.randn(n, heads, dim, generator=g) * 2 / math.sqrt(dim)).to(torch.bfloat16)
+    rel = torch.randn(heads, 41, generator=g) * 2
+    sink = torch.randn(heads, generator=g)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=CUDA)
+    want = torch.zeros(n, heads, vdim, dtype=torch.float64)
+    for e, c in enumerate(contexts):
+        for h in range(heads):
+            kh = h // (heads // kv_heads)
+            dist = (c - 1 - torch.arange(c)).clamp(max=40)
+            scores = (k_all[e][:, kh].double() @ q[e, h].double()) * 0.7 + rel[h].double()[dist]
+            top = max(float(scores.max()), float(sink[h]))
+            w = torch.exp(scores - top)
+            want[e, h] = (w[:, None] * v_all[e][:, kh].double()).sum(0) / (w.sum() + math.exp(float(sink[h]) - top))
+    got = {}
+    for splits in (1, 2, 3, 7, None):
+        out = torch.empty(n, heads * vdim, dtype=torch.bfloat16, device=CUDA)
+        ops.pooled_window_attention(q.view(n, -1).cuda(), out, i32(list(range(n + 1))), i32([c - 1 for c in contexts]), i32(list(range(n))),
+                                    keys_d, values_d, table.cuda(), None, None, None, n, 1, heads, kv_heads, window=1 << 30, pool=0,
+                                    scale=0.7, sink=sink.cuda(), rel_bias=rel.cuda().contiguous(), max_kv_len=max(contexts), splits=splits)
+        got[splits] = out.cpu().double().view(n, heads, vdim)
+        assert torch.isfinite(got[splits]).all()
+        assert (got[splits] - want).abs().max() <= 0.02 * want.abs().max(), splits
+    for splits in (2, 3, 7, None):
+        assert (got[splits] - got[1]).abs().max() <= 0.01 * want.abs().max()
+
+
 def test_the_bias_table_by_distance():
     """Rows by distance: one each below half the table, then logarithmic steps up to the last distance, the last row beyond."""
     from torchinferno_b200.parts.biased_attention import distance_buckets

@@ -496,7 +496,7 @@ def run_biased_attention(args) -> None:
             flops, moved = None, n * ctx * k * (d + v) * 2
         for name, bias in (("biased_attention", rel), ("the same without the bias", None)):
             fn = lambda: ops.pooled_window_attention(q, out, q_start, kv_start, slots, keys, values, table, None, None, None, n_entries,
-                                                     max_q, h, k, window=1 << 30, pool=0, scale=0.09, rel_bias=bias)
+                                                     max_q, h, k, window=1 << 30, pool=0, scale=0.09, rel_bias=bias, max_kv_len=ctx)
             report(f"{name}[{mode}]", timer(fn), flops=flops, bytes_moved=moved, entries=n_entries, context=ctx, heads=h, kv_heads=k,
                    head_dim=d, value_dim=v, bias_max=args.bias_max)
     n = args.tokens

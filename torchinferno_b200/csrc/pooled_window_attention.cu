@@ -201,6 +201,7 @@ struct PwaArgs {
   PwaCache tokens, blocks;
   int group_chunk, q_tile;
   int* error_word;
+  float* partial; int n_splits; int n_tokens;              // a step of single tokens whose contexts are shared out over blocks
 };
 
 template <typename T, int DPL>
@@ -431,7 +432,9 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int gc = min(a.group_chunk, group - g0);
   const int row0 = a.q_start[entry];
   const int q_len = a.q_start[entry + 1] - row0;
-  const int t0 = blockIdx.x * a.q_tile;
+  // (with the contexts shared out, blockIdx.x counts the parts of a context, and the block's rows are the entry's only ones)
+  const bool shared_out = WT && a.n_splits > 1;
+  const int t0 = shared_out ? 0 : blockIdx.x * a.q_tile;
   if (t0 >= q_len) return;
   const int nt = min(a.q_tile, q_len - t0);
   const int nrows = nt * gc;
@@ -448,6 +451,12 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int steps_b = (n_blocks + kPmKeys - 1) / kPmKeys;
   const int s_lo = first_key / kPmKeys, s_hi = last_pos / kPmKeys;
   const int steps = steps_b + (s_hi - s_lo + 1);
+  int step_lo = 0, step_hi = steps;                   // this block's share of the tiles
+  if (shared_out) {
+    const int per = (steps + a.n_splits - 1) / a.n_splits;
+    step_lo = min(steps, (int)blockIdx.x * per);
+    step_hi = min(steps, step_lo + per);
+  }
 
   // where key j of a tile lives: its page's first element and its row in the page
   auto locate = [&](int stage, int step, int j) {
@@ -521,6 +530,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   float factor[2], m[2], l[2];
   bool live[2];
   const float* rel[2];               // the row's head's biases by distance, or null
+  float rel_far[2];                  // the bias of every distance from the table's last on, in units of ln 2
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = row_base + g8 + 8 * h;
@@ -531,6 +541,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     seen[h] = a.pool > 0 ? lo[h] / a.pool : 0;       // blocks 0 .. seen - 1 lie wholly behind the window
     factor[h] = a.scale * (a.temp ? a.temp[kvh * group + g0 + g] : 1.f) * kLog2e;
     rel[h] = a.rel_bias ? a.rel_bias + (size_t)(kvh * group + g0 + g) * a.rel_span : nullptr;
+    rel_far[h] = rel[h] ? rel[h][a.rel_span - 1] * kLog2e : 0.f;
     m[h] = -CUDART_INF_F;
     l[h] = 0.f;
   }
@@ -579,7 +590,11 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
           const int idx = base + n * 8 + 2 * t4 + (c & 1);
           const bool allowed = live[h] && (pooled ? idx < seen[h] : (idx <= qpos[h] && idx >= lo[h]));
           s[n][c] = allowed ? s[n][c] * factor[h] : -CUDART_INF_F;
-          if (rel[h] && allowed && !pooled) s[n][c] = fmaf(rel[h][min(qpos[h] - idx, a.rel_span - 1)], kLog2e, s[n][c]);
+          if (rel[h] && allowed && !pooled) {
+            // (a tile that lies wholly beyond the table's last distance reads nothing)
+            const int dist = qpos[h] - idx;
+            s[n][c] = dist >= a.rel_span - 1 ? s[n][c] + rel_far[h] : fmaf(rel[h][dist], kLog2e, s[n][c]);
+          }
         }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -640,17 +655,17 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     // Few rows: only one warp would have work.  So the four warps each take one tile of a set of four (all in flight
     // at once), with sums of their own, which are added in the order of the warps afterwards.
     static_assert(!WT || ST == kPmThreads / 32, "a stage a warp");
-    for (int first = 0; first < steps; first += ST) {
+    for (int first = step_lo; first < step_hi; first += ST) {
       // (all of the set's page numbers are asked for at once, then all of its tiles)
       for (int e = tid; e < ST * kPmKeys; e += kPmThreads)
-        if (first + e / kPmKeys < steps) locate(e / kPmKeys, first + e / kPmKeys, e % kPmKeys);
+        if (first + e / kPmKeys < step_hi) locate(e / kPmKeys, first + e / kPmKeys, e % kPmKeys);
       __syncthreads();
 #pragma unroll
       for (int s0 = 0; s0 < ST; ++s0)
-        if (first + s0 < steps) copy(s0, first + s0);
+        if (first + s0 < step_hi) copy(s0, first + s0);
       cp_async_wait<0>();
       __syncthreads();
-      if (first + warp < steps) tile(warp, first + warp);
+      if (first + warp < step_hi) tile(warp, first + warp);
       __syncthreads();    // the stages are free for the next set
     }
   } else {
@@ -716,6 +731,25 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
       }
     }
     __syncthreads();      // the partial sums are read: the place is free for the rows' sums
+    if (shared_out) {
+      // this part's maxima, denominators and sums (in units of ln 2, not yet divided) go to the kernel that adds the parts
+      if (warp == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = g8 + 8 * h;
+          if (!live[h]) continue;
+          const int t = r / gc, g = r - t * gc;
+          float* dst = a.partial + (((size_t)blockIdx.x * a.n_tokens + (row0 + t)) * a.heads + (kvh * group + g0 + g)) * (DV + 2);
+          if (t4 == 0) { dst[0] = m[h]; dst[1] = l[h]; }
+#pragma unroll
+          for (int n = 0; n < DV / 8; ++n) {
+            dst[2 + n * 8 + 2 * t4] = o[n][2 * h];
+            dst[2 + n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+          }
+        }
+      }
+      return;
+    }
   }
   // the rows' sums, divided by the softmax's denominator (with the number that has no key), into shared memory
   float* o_s = reinterpret_cast<float*>(k_s);           // [64][DV] floats over the key and value stages, which adjoin
@@ -784,6 +818,41 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   }
 }
 
+// Adds the parts of a context that was shared out over blocks, in the order of the parts: out = sum_s o_s 2^(m_s - top)
+// / (sum_s l_s 2^(m_s - top) + 2^(sink - top)).  One block per token, a warp per head.
+template <int DV>
+__global__ void __launch_bounds__(128) pwa_merge_kernel(__nv_bfloat16* __restrict__ out, PwaArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int token = blockIdx.x, lane = threadIdx.x & 31;
+  for (int head = threadIdx.x >> 5; head < a.heads; head += blockDim.x >> 5) {
+    float top = -CUDART_INF_F;
+    for (int s = 0; s < a.n_splits; ++s)
+      top = fmaxf(top, a.partial[(((size_t)s * a.n_tokens + token) * a.heads + head) * (DV + 2)]);
+    float denom = 0.f, acc[DV / 32];
+#pragma unroll
+    for (int j = 0; j < DV / 32; ++j) acc[j] = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) {
+      const float* part = a.partial + (((size_t)s * a.n_tokens + token) * a.heads + head) * (DV + 2);
+      if (part[0] == -CUDART_INF_F) continue;
+      const float weight = exp2f(part[0] - top);
+      denom = fmaf(part[1], weight, denom);
+#pragma unroll
+      for (int j = 0; j < DV / 32; ++j) acc[j] = fmaf(part[2 + lane + 32 * j], weight, acc[j]);
+    }
+    float scale = 1.f;
+    if (a.sink) {
+      const float sink = a.sink[head] * kLog2e, high = fmaxf(top, sink);
+      scale = exp2f(top - high);
+      denom = denom * scale + exp2f(sink - high);
+    }
+    const float inv = denom > 0.f ? scale / denom : 0.f;
+#pragma unroll
+    for (int j = 0; j < DV / 32; ++j)
+      if (lane + 32 * j < a.vdim) out[(size_t)token * a.heads * a.vdim + (size_t)head * a.vdim + lane + 32 * j] = __float2bfloat16_rn(acc[j] * inv);
+  }
+}
+
 template <int DK, int DV, int ST, bool WT>
 static int pwa_launch_mma_staged(const void* q, void* out, const PwaArgs& a, dim3 grid, cudaStream_t stream) {
   static_assert(kPmRows * DV * sizeof(float) <= ST * kPmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the rows' sums fit the stages");
@@ -808,10 +877,36 @@ static int pwa_launch_mma(const void* q, void* out, PwaArgs a, int n_entries, in
   a.q_tile = kPmRows / a.group_chunk;
   const int chunks = (group + a.group_chunk - 1) / a.group_chunk;
   if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
-  const dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, a.kv_heads * chunks);
-  if ((int64_t)max_q_len * a.group_chunk <= 16) return pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+  dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, a.kv_heads * chunks);
+  if ((int64_t)max_q_len * a.group_chunk <= 16) {
+    if (a.n_splits > 1) {
+      // single tokens whose contexts are shared out over n_splits blocks each; a second kernel adds the parts
+      if (max_q_len != 1 || !a.partial || a.vfreq || a.gate) return TIB_E_ARG;
+      grid.x = a.n_splits;
+      const int status = pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+      if (status != TIB_OK) return status;
+      TIB_LAUNCH_DEPENDENT(pwa_merge_kernel<DV>, a.n_tokens, 128, 0, stream, (__nv_bfloat16*)out, a);
+      return TIB_OK;
+    }
+    return pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+  }
+  a.n_splits = 1;
   return pwa_launch_mma_staged<DK, DV, 2, false>(q, out, a, grid, stream);
 }
+
+// How many blocks a step of `n_entries` single tokens should share each context of up to `max_kv_len` visible keys out
+// over (1: none), and the floats of scratch a part of one (token, head) row takes.
+TIB_API int tib_pooled_window_attention_splits(int n_entries, int heads, int kv_heads, int visible) {
+  const int group = heads / (kv_heads < 1 ? 1 : kv_heads);
+  if (group > 16) return 1;                            // (more than sixteen rows a block: the other form of the kernel)
+  const int blocks = n_entries * kv_heads;
+  const int sets = ceil_div(ceil_div(visible < 1 ? 1 : visible, kPmKeys) + 1, 4);      // rounds of four tiles
+  int splits = 2 * 148 / (blocks < 1 ? 1 : blocks);
+  if (splits > sets) splits = sets;
+  if (splits > 32) splits = 32;
+  return splits < 1 ? 1 : splits;
+}
+TIB_API int tib_pooled_window_attention_part_floats(int vdim) { return (vdim <= 64 ? 64 : 128) + 2; }
 
 // Whether the tensor-core kernel takes these shapes (bf16; rows of 16-byte pieces in every array it copies from).
 static bool pwa_mma_takes(const PwaArgs& a, const void* q) {
@@ -891,7 +986,9 @@ TIB_API int tib_pool_blocks(const void* k_pages, const void* v_pages, const int*
 // q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, heads * vdim] logits (row stride ld_gate, its
 // own dtype) or null; temp, sink: [heads] fp32 or null; vfreq: [vdim / 2] fp32 or null.  pool 0: the window alone.
 // rel_bias: [heads, rel_span] fp32 or null: rel_bias[h, min(i - j, rel_span - 1)] is added to the score of token j (not
-// multiplied by scale or temp; blocks get none).
+// multiplied by scale or temp; blocks get none).  n_splits > 1 (a step of single tokens only, bf16 on the tensor cores, no
+// turned values and no gate): every context is shared out over n_splits blocks, whose sums go through `partial`
+// [n_splits, n_tokens, heads, part floats] to a second kernel; n_tokens: rows of q.
 // force_simt: the CUDA-core kernel also where the tensor-core kernel would take the step.
 TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_start, const int* kv_start, const int* slots,
                                         const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
@@ -900,8 +997,8 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
                                         int64_t b_page_stride, int b_num_pages, int n_entries, int max_q_len, int heads,
                                         int kv_heads, int dim, int vdim, int window, int pool, float scale, const float* temp,
                                         const float* sink, const float* vfreq, const void* gate, int gate_dtype, int64_t ld_gate,
-                                        const float* rel_bias, int rel_span, int* error_word, int dtype, int force_simt,
-                                        cudaStream_t stream) {
+                                        const float* rel_bias, int rel_span, float* partial, int n_splits, int n_tokens,
+                                        int* error_word, int dtype, int force_simt, cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!q || !out || !q_start || !kv_start || !slots || !k_pages || !v_pages || !block_table) return TIB_E_ARG;
   if (pool > 0 && (!bk_pages || !bv_pages || !b_table || b_page_size < 1)) return TIB_E_ARG;
@@ -916,6 +1013,7 @@ TIB_API int tib_pooled_window_attention(const void* q, void* out, const int* q_s
   a.tokens = pwa_cache(const_cast<void*>(k_pages), const_cast<void*>(v_pages), block_table, table_stride, page_size, page_stride, num_pages);
   a.blocks = pwa_cache(const_cast<void*>(bk_pages), const_cast<void*>(bv_pages), b_table, b_table_stride, b_page_size, b_page_stride, b_num_pages);
   a.error_word = error_word;
+  a.partial = partial; a.n_splits = n_splits > 1 ? n_splits : 1; a.n_tokens = n_tokens;
   const int group = heads / kv_heads;
   a.group_chunk = group < kPwaRows ? group : kPwaRows;
   a.q_tile = kPwaRows / a.group_chunk;

@@ -126,7 +126,8 @@ def lib() -> ctypes.CDLL:
                    "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
                    "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence",
                    "tib_softcap_f32", "tib_short_conv", "tib_ssd_scan", "tib_ssd_scan_max_state", "tib_ssd_scan_run", "tib_gated_group_norm",
-                   "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention", "tib_hyper_step"):
+                   "tib_rotary_kv_append", "tib_pool_blocks", "tib_pooled_window_attention", "tib_hyper_step",
+                   "tib_pooled_window_attention_splits", "tib_pooled_window_attention_part_floats"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -1387,13 +1388,15 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
                             temp: torch.Tensor | None = None, sink: torch.Tensor | None = None,
                             value_freq: torch.Tensor | None = None, gate: torch.Tensor | None = None,
                             error_word: torch.Tensor | None = None, force_simt: bool = False,
-                            rel_bias: torch.Tensor | None = None) -> torch.Tensor:
+                            rel_bias: torch.Tensor | None = None, max_kv_len: int = 0, splits: int | None = None) -> torch.Tensor:
     """Per head, out[i] = sigmoid(gate[i]) * turn_back_i(sum_j w_ij v_j + sum_b w_ib V_b): softmax weights over the tokens j
     with 0 <= i - j < window and the blocks b of ``pool`` positions with b * pool + pool - 1 <= i - window (their means K_b,
     V_b from the strided pages), scores q . k * scale * temp[h], exp(sink[h]) added to the denominator; turn_back undoes at
     position i the rotation the values were cached with (``value_freq``; None: none).  ``pool`` 0: the window alone.
     ``rel_bias`` [heads, span] fp32: rel_bias[h, min(i - j, span - 1)] is added to the score of token j (as it is: neither
-    ``scale`` nor ``temp`` multiplies it).
+    ``scale`` nor ``temp`` multiplies it).  A step of single tokens only on the tensor cores (no turned values, no gate) that
+    names the longest context (``max_kv_len``) shares every context's visible keys out over ``splits`` blocks (None: enough
+    to fill the GPU) whose sums a second small kernel adds in a fixed order.
     bfloat16 steps run on the tensor cores when the head sizes are multiples of 8 up to 128, unless ``force_simt``."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim = keys.shape[3], values.shape[3]
@@ -1420,6 +1423,18 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
         _need(rel_bias, "rel_bias", torch.float32)
         if rel_bias.dim() != 2 or rel_bias.shape[0] != heads or rel_bias.shape[1] < 1:
             raise KernelError("pooled_window_attention: rel_bias must be [heads, span]")
+    partial, n_splits = None, 1
+    if (max_q_len == 1 and n == n_entries and max_kv_len > 0 and q.dtype == torch.bfloat16 and not force_simt
+            and value_freq is None and gate is None and dim % 8 == 0 and vdim % 8 == 0 and dim <= 128 and vdim <= 128
+            and heads // kv_heads <= 16):
+        n_splits = splits if splits is not None else int(lib().tib_pooled_window_attention_splits(
+            c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(min(window, max_kv_len) + (max_kv_len // pool if pool else 0))))
+        if n_splits > 1:
+            floats = int(lib().tib_pooled_window_attention_part_floats(c_int(vdim)))
+            partial = torch.empty((n_splits, n, heads, floats), dtype=torch.float32, device=q.device)
+            count_launches(1)
+        else:
+            n_splits = 1
     _check("pooled_window_attention", lib().tib_pooled_window_attention(
         _ptr(q), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(keys), _ptr(values), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), c_int64(page_stride), c_int(num_pages),
@@ -1427,8 +1442,8 @@ def pooled_window_attention(q: torch.Tensor, out: torch.Tensor, q_start: torch.T
         _ptr(block_block_table if pool > 0 else None), c_int(b_table_stride), c_int(b_page_size), c_int64(b_stride), c_int(b_pages),
         c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(window), c_int(pool),
         c_float(scale), _ptr(temp), _ptr(sink), _ptr(value_freq), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
-        c_int64(ld_gate), _ptr(rel_bias), c_int(rel_bias.shape[1] if rel_bias is not None else 0), _ptr(error_word),
-        c_int(_code(q.dtype)), c_int(int(force_simt)), _stream()))
+        c_int64(ld_gate), _ptr(rel_bias), c_int(rel_bias.shape[1] if rel_bias is not None else 0), _ptr(partial),
+        c_int(n_splits), c_int(n), _ptr(error_word), c_int(_code(q.dtype)), c_int(int(force_simt)), _stream()))
     return out
 
 
@@ -1442,10 +1457,11 @@ def hyper_step(streams: torch.Tensor, *, y: torch.Tensor | None = None, mix: tor
     (all streams from the old ones), then with ``in_weights`` the read u = sum_s in_weights[s] x_s into ``out``: as fp32
     sums, or with ``tanh_norm`` = (alpha, weight, bias) as tanh(alpha u) * weight + bias in ``out``'s type.  With ``rows``
     (int32 token rows) only those rows are read, ``out`` has one row per index and nothing is stored."""
-    _need(streams, "streams", torch.float32)
-    if streams.dim() != 3:
-        raise KernelError("hyper_step: streams must be [S, tokens, width]")
+    if not streams.is_cuda or streams.dtype != torch.float32 or streams.dim() != 3:
+        raise KernelError("hyper_step: streams must be a CUDA fp32 tensor [S, tokens, width]")
     count, n, width = streams.shape
+    if streams.stride(2) != 1 or streams.stride(1) != width:
+        raise KernelError("hyper_step: every stream must be contiguous rows (the streams may lie apart)")
     if y is not None:
         _rows_of(y, "y", width)
         if y.shape[0] != n or mix is None or out_weights is None:

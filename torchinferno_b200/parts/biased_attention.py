@@ -122,7 +122,7 @@ class BiasedAttention(Mixer):
         ops.pooled_window_attention(q, out, batch.q_start, batch.kv_start, batch.slots, kv.keys, kv.values, kv.block_table,
                                     None, None, None, batch.n_entries, batch.max_q_len, h, g,
                                     window=self.window or NO_WINDOW, pool=0, scale=self.scale,
-                                    rel_bias=self.bias_by_distance, error_word=ctx.error_word)
+                                    rel_bias=self.bias_by_distance, error_word=ctx.error_word, max_kv_len=batch.max_kv_len)
         return linear(out, self.o_weight)
 
 
