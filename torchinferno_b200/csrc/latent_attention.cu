@@ -9,7 +9,8 @@
 //
 //   latent_append     per token: c = rmsnorm(dkv[:rank]) * w, r = rotate(dkv[rank:]), both stored in the token's
 //                     page; qr_j = rotate(q_j[dim:]) written behind a_j in the folded query rows.  Rotary pairs
-//                     are (2i, 2i+1), angle = position * inv_freq[i] in fp32, on the first 2 * n_freq elements.
+//                     are (2i, 2i+1), or (i, i + n_freq), angle = position * inv_freq[i] in fp32, on the first
+//                     2 * n_freq elements.
 //   latent_attention  causal softmax attention of the folded queries [tokens, heads, rank + rot] (fp32) over
 //                     the paged latent rows; out [tokens, heads, rank] (fp32).  Two kernels:
 //                     - CUDA cores, fp32 throughout (the 32-bit path, and every shape): one warp owns one

@@ -10,14 +10,17 @@
 //   attention          query i sees the tokens j with 0 <= i - j < window, and the blocks b with
 //                      b * pool + pool - 1 <= i - window; score = q . k * scale * temp[h]; one softmax over both, with
 //                      exp(sink[h]) added to its denominator; the head's sum of values is turned back by -i over the
-//                      value pairs and multiplied element by element by sigmoid(gate)
+//                      value pairs and multiplied element by element by sigmoid(gate).  Optionally a learned number per
+//                      head and distance, rel_bias[h][min(i - j, span - 1)], is added to a token's score (a design
+//                      without window or blocks passes a window beyond every position and pool 0)
 //
 // Scores, the softmax, the sums over values, the turning back and the gate are fp32.  Two kernels.  On the CUDA cores
 // (32-bit, any head size) one warp owns one (query token, query head) row from start to end and walks
 // first the blocks, then the tokens, 32 at a time, aligned to absolute block numbers / positions, in rising order: a
 // row's arithmetic depends only on its own position, never on how the batch was cut, which rows share the thread
 // block, or which pages hold the keys.  On the tensor cores (bf16, head sizes that are multiples of 8) the same
-// walk runs in tiles of 64 with mma.sync, see below.
+// walk runs in tiles of 64 with mma.sync, see below; a step of single tokens may share each context's tiles out over
+// several blocks, whose sums a small second kernel adds in the order of the parts.
 #include "mma.cuh"
 #include <math_constants.h>
 
