@@ -74,7 +74,7 @@ VE = {
     "layers": [
         layer("latent_attention", latent(8, 16, 16, 16, 64, 32, 0.18, base=10000.0), dense(48)),
         layer("latent_attention", latent(2, 8, 2, 4, 6, 3, 0.3, base=10.0), None),
-        layer("latent_attention", latent(4, 32, 16, 24, 64, 48, 0.12, base=1e6), moe(8, 4, 4, 32, count=4, keep=3)),
+        layer("latent_attention", latent(4, 32, 16, 24, 64, 48, 0.12, base=1e6), moe(10, 5, 4, 32, count=5, keep=3)),
     ],
 }
 CONFIGS = {"VA": (VA, 41), "VB": (VB, 42), "VC": (VC, 43), "VD": (VD, 44), "VE": (VE, 45)}
