@@ -411,9 +411,15 @@ static int pwa_launch(const void* q, void* out, const PwaArgs& a, int n_entries,
 // scores in units of ln 2; the weights enter the second product as a high bf16 part plus the remainder, so that they
 // keep 16 bits.  The rows' sums then pass through shared memory, where pairs (m, m + vdim / 2) meet for the turning back.
 constexpr int kPmRows = 64, kPmKeys = 64, kPmThreads = 128;
+// Tiles a block of few rows has in flight (a warp each) when the contexts are shared out over blocks.  Two: the stages are
+// 87 KB and two blocks share an SM, so that one block's loads run under the other's arithmetic; with four (156 KB, a block
+// an SM: the form for contexts that are not shared out) nothing overlaps.
+constexpr int kPmFewRowStages = 2;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DK, int DV, int ST, bool WT>
+// REL: the kernel knows the table of biases by distance and contexts shared out over blocks (without it, it is the kernel
+// as the designs without either have always run it, register for register).
+template <int DK, int DV, int ST, bool WT, bool REL>
 __global__ void __launch_bounds__(kPmThreads)
 pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, PwaArgs a) {
   pdl_wait();
@@ -436,7 +442,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int row0 = a.q_start[entry];
   const int q_len = a.q_start[entry + 1] - row0;
   // (with the contexts shared out, blockIdx.x counts the parts of a context, and the block's rows are the entry's only ones)
-  const bool shared_out = WT && a.n_splits > 1;
+  const bool shared_out = REL && WT && a.n_splits > 1;
   const int t0 = shared_out ? 0 : blockIdx.x * a.q_tile;
   if (t0 >= q_len) return;
   const int nt = min(a.q_tile, q_len - t0);
@@ -543,8 +549,8 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     lo[h] = max(0, qpos[h] - a.window + 1);
     seen[h] = a.pool > 0 ? lo[h] / a.pool : 0;       // blocks 0 .. seen - 1 lie wholly behind the window
     factor[h] = a.scale * (a.temp ? a.temp[kvh * group + g0 + g] : 1.f) * kLog2e;
-    rel[h] = a.rel_bias ? a.rel_bias + (size_t)(kvh * group + g0 + g) * a.rel_span : nullptr;
-    rel_far[h] = rel[h] ? rel[h][a.rel_span - 1] * kLog2e : 0.f;
+    rel[h] = REL && a.rel_bias ? a.rel_bias + (size_t)(kvh * group + g0 + g) * a.rel_span : nullptr;
+    rel_far[h] = REL && rel[h] ? rel[h][a.rel_span - 1] * kLog2e : 0.f;
     m[h] = -CUDART_INF_F;
     l[h] = 0.f;
   }
@@ -593,12 +599,29 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
           const int idx = base + n * 8 + 2 * t4 + (c & 1);
           const bool allowed = live[h] && (pooled ? idx < seen[h] : (idx <= qpos[h] && idx >= lo[h]));
           s[n][c] = allowed ? s[n][c] * factor[h] : -CUDART_INF_F;
-          if (rel[h] && allowed && !pooled) {
-            // (a tile that lies wholly beyond the table's last distance reads nothing)
-            const int dist = qpos[h] - idx;
-            s[n][c] = dist >= a.rel_span - 1 ? s[n][c] + rel_far[h] : fmaf(rel[h][dist], kLog2e, s[n][c]);
+        }
+      if (REL && a.rel_bias && !pooled) {
+        // the learned number of every (head, distance), without a branch per score: a masked score stays minus infinity
+        // whatever is added, so its distance is clamped into the table; a row whose every key of the tile lies beyond
+        // the table's last distance reads nothing
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d0 = qpos[h] - base - 2 * t4;            // distance to the first of this thread's keys
+          if (d0 - (kPmKeys - 1) >= a.rel_span - 1) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+              s[n][2 * h] += rel_far[h];
+              s[n][2 * h + 1] += rel_far[h];
+            }
+          } else {
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+              for (int b = 0; b < 2; ++b)
+                s[n][2 * h + b] = fmaf(rel[h][min(max(d0 - n * 8 - b, 0), a.rel_span - 1)], kLog2e, s[n][2 * h + b]);
           }
         }
+      }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float mx = -CUDART_INF_F;
@@ -655,9 +678,9 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
   };
   if (WT) {
-    // Few rows: only one warp would have work.  So the four warps each take one tile of a set of four (all in flight
+    // Few rows: only one warp would have work.  So ST of the warps each take one tile of a set of ST (all in flight
     // at once), with sums of their own, which are added in the order of the warps afterwards.
-    static_assert(!WT || ST == kPmThreads / 32, "a stage a warp");
+    static_assert(!WT || ST <= kPmThreads / 32, "at most a stage a warp");
     for (int first = step_lo; first < step_hi; first += ST) {
       // (all of the set's page numbers are asked for at once, then all of its tiles)
       for (int e = tid; e < ST * kPmKeys; e += kPmThreads)
@@ -668,7 +691,7 @@ pwa_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         if (first + s0 < step_hi) copy(s0, first + s0);
       cp_async_wait<0>();
       __syncthreads();
-      if (first + warp < step_hi) tile(warp, first + warp);
+      if (warp < ST && first + warp < step_hi) tile(warp, first + warp);
       __syncthreads();    // the stages are free for the next set
     }
   } else {
@@ -856,11 +879,11 @@ __global__ void __launch_bounds__(128) pwa_merge_kernel(__nv_bfloat16* __restric
   }
 }
 
-template <int DK, int DV, int ST, bool WT>
+template <int DK, int DV, int ST, bool WT, bool REL>
 static int pwa_launch_mma_staged(const void* q, void* out, const PwaArgs& a, dim3 grid, cudaStream_t stream) {
   static_assert(kPmRows * DV * sizeof(float) <= ST * kPmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the rows' sums fit the stages");
   const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kPmRows * (DK + 8) + ST * (size_t)kPmKeys * (DK + 8) + ST * (size_t)kPmKeys * (DV + 8));
-  auto kern = pwa_attention_mma_kernel<DK, DV, ST, WT>;
+  auto kern = pwa_attention_mma_kernel<DK, DV, ST, WT, REL>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -886,15 +909,18 @@ static int pwa_launch_mma(const void* q, void* out, PwaArgs a, int n_entries, in
       // single tokens whose contexts are shared out over n_splits blocks each; a second kernel adds the parts
       if (max_q_len != 1 || !a.partial || a.vfreq || a.gate) return TIB_E_ARG;
       grid.x = a.n_splits;
-      const int status = pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+      const int status = pwa_launch_mma_staged<DK, DV, kPmFewRowStages, true, true>(q, out, a, grid, stream);
       if (status != TIB_OK) return status;
       TIB_LAUNCH_DEPENDENT(pwa_merge_kernel<DV>, a.n_tokens, 128, 0, stream, (__nv_bfloat16*)out, a);
       return TIB_OK;
     }
-    return pwa_launch_mma_staged<DK, DV, 4, true>(q, out, a, grid, stream);
+    a.n_splits = 1;
+    if (a.rel_bias) return pwa_launch_mma_staged<DK, DV, kPmFewRowStages, true, true>(q, out, a, grid, stream);
+    return pwa_launch_mma_staged<DK, DV, 4, true, false>(q, out, a, grid, stream);
   }
   a.n_splits = 1;
-  return pwa_launch_mma_staged<DK, DV, 2, false>(q, out, a, grid, stream);
+  if (a.rel_bias) return pwa_launch_mma_staged<DK, DV, 2, false, true>(q, out, a, grid, stream);
+  return pwa_launch_mma_staged<DK, DV, 2, false, false>(q, out, a, grid, stream);
 }
 
 // How many blocks a step of `n_entries` single tokens should share each context of up to `max_kv_len` visible keys out
@@ -903,7 +929,7 @@ TIB_API int tib_pooled_window_attention_splits(int n_entries, int heads, int kv_
   const int group = heads / (kv_heads < 1 ? 1 : kv_heads);
   if (group > 16) return 1;                            // (more than sixteen rows a block: the other form of the kernel)
   const int blocks = n_entries * kv_heads;
-  const int sets = ceil_div(ceil_div(visible < 1 ? 1 : visible, kPmKeys) + 1, 4);      // rounds of four tiles
+  const int sets = ceil_div(ceil_div(visible < 1 ? 1 : visible, kPmKeys) + 1, kPmFewRowStages);      // rounds of tiles
   int splits = 2 * 148 / (blocks < 1 ? 1 : blocks);
   if (splits > sets) splits = sets;
   if (splits > 32) splits = 32;
