@@ -119,9 +119,9 @@ class VofidraConfig:
         eps = _number(_need(data, "norm", where), "eps", "norm")
         if not eps > 0:
             raise ConfigError("config.json: norm.eps must be positive")
-        cap = data.get("logit_softcap")
-        if cap is not None and not float(cap) > 0:
-            raise ConfigError("config.json: logit_softcap must be positive when given")
+        cap = data.get("logit_softcap") or None          # (absent, null or 0: the logits are not capped)
+        if cap is not None and (isinstance(cap, bool) or not isinstance(cap, (int, float)) or not float(cap) > 0):
+            raise ConfigError("config.json: logit_softcap must be a positive number when given")
         return cls(vocab=_positive(data, "vocab", where), width=_positive(data, "width", where),
                    streams=_positive(data, "streams", where), layers=typed, eps=eps,
                    logit_softcap=None if cap is None else float(cap), raw=dict(data))
