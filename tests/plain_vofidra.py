@@ -37,7 +37,7 @@ def read_model_folder(folder, dtype=F):
 
 # ------------------------------------------------------------- small pieces
 def tanh_norm(x, w, name):
-    """tanh(alpha x) * weight + bias; no mean, no variance.  ``name`` + '.alpha' is a scalar, ``name`` + '.b' the bias."""
+    """tanh(alpha x) * weight + bias, element by element: no statistic of the row enters.  ``name`` + '.alpha' is a scalar, ``name`` + '.b' the bias."""
     return torch.tanh(w[name + ".alpha"] * x) * w[name] + w[name + ".b"]
 
 
@@ -77,7 +77,7 @@ def read_streams(x, into):
 
 
 def write_streams(x, mix, out, y):
-    """x_t <- sum_s mix[s, t] x_s + out[t] y, all streams from the old ones."""
+    """x_t <- sum_s mix[s, t] x_s + out[t] y, every stream from the values before the write."""
     return torch.einsum("st,snw->tnw", mix, x) + out[:, None, None] * y[None]
 
 
@@ -139,7 +139,7 @@ def gated_unit(h, w, p):
 
 def route(h, w, p, router, gaps=None):
     """(ids [T, top], weights [T, top]): softmax scores over experts and identity experts; the choice adds the correction
-    and looks only at the best ``keep`` of ``count`` groups of neighbours (a group's score is its largest choice score);
+    and is made among the members of the ``keep`` best of ``count`` equal runs of adjacent outputs (a run ranks by its best corrected score);
     the weights are the chosen scores without the correction, divided by their sum + 1e-20.  ``gaps`` (a list) receives
     per token the smallest margin by which a choice was made: between the last group kept and the first one dropped, and
     between the last output chosen and the first one left."""

@@ -565,7 +565,7 @@ def test_the_bias_table_by_distance():
     (1, 5, 2, 1, 1, 20), (7, 2, 4, 3, 2, 150)])
 def test_routed_gated_units_alone(dtype, experts, identity, top, count, keep, tokens):
     """Routed units alone, among them: every output chosen, top 1, more groups than choices, experts without tensors in
-    the majority, and corrections that make every choice score negative (an output of a dropped group must not come back
+    the majority, and corrections that make every corrected score negative (an output of a dropped group must not come back
     as a zero that beats them)."""
     need_gpu()
     from torchinferno_b200.parts.base import LayerContext, PartSpec, build_part

@@ -136,7 +136,7 @@ def test_plain_mechanisms_against_closed_forms():
     new = plain_vofidra.write_streams(x, mix, torch.zeros(2, dtype=torch.float64), y)
     assert torch.allclose(new[0], x[0]) and torch.allclose(new[1], 5 * x[0] + x[1])
     assert torch.allclose(plain_vofidra.read_streams(x, torch.tensor([2.0, -1.0], dtype=torch.float64)), 2 * x[0] - x[1])
-    # the tanh norm knows no mean or variance: a row and its double differ, and a large entry saturates at weight + bias
+    # the tanh norm takes no statistic of the row: a row and its double differ, and a large entry saturates at weight + bias
     w = {"n": torch.full((3,), 2.0, dtype=torch.float64), "n.b": torch.full((3,), 0.5, dtype=torch.float64),
          "n.alpha": torch.tensor(0.5, dtype=torch.float64)}
     row = torch.tensor([[0.2, -1.0, 400.0]], dtype=torch.float64)
@@ -154,7 +154,7 @@ def test_plain_mechanisms_against_closed_forms():
     # the temperature steps every `every` positions, counted from position every - 1
     temps = plain_vofidra.query_temperature(torch.arange(9), 0.5, 4)
     assert torch.allclose(temps, torch.tensor([1.0] * 3 + [1 + 0.5 * math.log(2)] * 4 + [1 + 0.5 * math.log(3)] * 2, dtype=torch.float64))
-    # routing: a dropped group's outputs cannot be chosen even when every kept choice score is negative; weights are made
+    # routing: a dropped group's outputs cannot be chosen even when every corrected score that is kept is negative; weights are made
     # from the scores without the correction; outputs past the experts hand the input through
     router = {"experts": 2, "identity": 2, "top": 2, "groups": {"count": 2, "keep": 1}}
     w = {"r.router": torch.tensor([[1.0], [0.0], [3.0], [-9.0]], dtype=torch.float64),

@@ -3,7 +3,7 @@
 // Instead of one residual x there are S copies x_1 .. x_S [S, tokens, width] in fp32.  A sublayer reads them through
 // one weighted sum and writes its output y back through a small matrix:
 //
-//   write   x_t <- sum_s mix[s, t] x_s + out_w[t] * y          all streams at once, from the old ones
+//   write   x_t <- sum_s mix[s, t] x_s + out_w[t] * y          every stream from the values before the write
 //   read    u = sum_s in_w[s] x_s;   rows = norm(u)
 //
 // One launch does a write (optional), then a read (optional) of the streams it has just made, element by element:

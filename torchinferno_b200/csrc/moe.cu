@@ -88,8 +88,8 @@ router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restr
 
 // ------------------------------------------------------------------- route
 // One warp per token.  score(e) = softmax(z)[e] or sigmoid(z[e]); the choice looks at score + correction[e] (when a
-// correction is given) and, with `groups` > 1, only at the experts of the `keep` groups of neighbours whose largest
-// choice score is best (an expert of another group cannot be chosen, whatever its score); the weights are made from the
+// correction is given) and, with `groups` > 1, only at the experts of the `keep` runs of adjacent experts whose best
+// corrected score ranks highest (an expert of another run is not eligible, whatever its score); the weights are made from the
 // scores without the correction.  Lowest index first among equals, for groups and for experts.
 constexpr int kRouteMaxGroups = 64;      // (two groups a lane)
 
@@ -468,7 +468,7 @@ TIB_API int tib_router_logits(const void* x, int x_dtype, int64_t ldx, const flo
 }
 
 // correction: [experts] fp32 added to the scores for the choice only, or null; groups > 1 with keep < groups: the experts
-// form `groups` equal runs of neighbours and only those of the best `keep` runs can be chosen.
+// are cut into `groups` equal runs of adjacent ones and only members of the best `keep` runs are eligible.
 TIB_API int tib_moe_route(const float* logits, int64_t ld, int tokens, int experts, int top, int sigmoid_scores, int normalize,
                           float norm_eps, const float* correction, int groups, int keep, int* ids, float* weights,
                           cudaStream_t stream) {

@@ -959,8 +959,8 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, w
               correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1) -> None:
     """From fp32 router logits (the first ``experts`` columns of ``logits``): the ``top`` best experts of every token and
     their weights.  ``correction`` [experts] is added to the scores for the choice only (the weights are made from the
-    scores themselves); with ``groups`` > 1 the experts form that many equal runs of neighbours, and only those of the
-    ``keep`` runs whose best choice score is largest can be chosen."""
+    scores themselves); with ``groups`` > 1 the outputs are cut into that many equal runs of adjacent ones, every run is
+    ranked by the best corrected score in it, and only members of the ``keep`` best runs are eligible."""
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1 or logits.shape[1] < experts:
         raise KernelError("moe_route: logits must be 2-D fp32 with unit inner stride and at least `experts` columns")
     _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32)
@@ -1454,7 +1454,7 @@ def hyper_step(streams: torch.Tensor, *, y: torch.Tensor | None = None, mix: tor
                rows: torch.Tensor | None = None, tanh_norm: tuple[float, torch.Tensor, torch.Tensor] | None = None
                ) -> torch.Tensor | None:
     """On streams [S, tokens, width] (fp32), in one launch: with ``y`` the write x_t <- sum_s mix[s, t] x_s + out_weights[t] y
-    (all streams from the old ones), then with ``in_weights`` the read u = sum_s in_weights[s] x_s into ``out``: as fp32
+    (every stream from the values before the write), then with ``in_weights`` the read u = sum_s in_weights[s] x_s into ``out``: as fp32
     sums, or with ``tanh_norm`` = (alpha, weight, bias) as tanh(alpha u) * weight + bias in ``out``'s type.  With ``rows``
     (int32 token rows) only those rows are read, ``out`` has one row per index and nothing is stored."""
     if not streams.is_cuda or streams.dtype != torch.float32 or streams.dim() != 3:

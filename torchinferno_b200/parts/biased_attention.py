@@ -2,7 +2,7 @@
 through a query temperature.
 
 q = W_q x, k = W_k x, v = W_v x (no biases); every q and k head is divided by its root mean square (``qk_norm_eps``)
-and multiplied by a weight of ``dim`` numbers that all heads share (``q.norm`` / ``k.norm``; plain, not one-plus);
+and multiplied by a weight of ``dim`` numbers that all heads share (``q.norm`` / ``k.norm``, multiplied in as stored: no 1 is added);
 with ``temp_every`` = E > 0 the query at position p is also multiplied by 1 + ``temp_coef`` * ln(floor((p + 1) / E) + 1);
 score(i, j) = q_i . k_j * ``scale`` + rel[bucket(i - j), h], where ``rel`` is the layer's table of B rows (one number per
 head in each; the checkpoint's tensor says how many, ``buckets`` is what random weights get) and, with ``bias_max`` = D
@@ -12,7 +12,7 @@ and half = B / 2,
               = min(B - 1, half + floor(ln(n / half) / ln(D / half) * (B - half)))   otherwise
 
 (small distances have a row each, larger ones share rows on a logarithmic scale, everything from D on the last row);
-``scale`` does not multiply the bias.  Causal softmax (optionally inside a ``window``); query head h reads key/value
+the bias is added after the scaling.  Causal softmax (optionally inside a ``window``); query head h reads key/value
 head h // (heads / kv_heads); keys may be wider or narrower than values; then the output projection.
 
 When the model is bound the table is laid out by distance, [heads, D + 1] (distances from D on read the last entry),

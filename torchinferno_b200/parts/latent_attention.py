@@ -4,8 +4,8 @@ From the layer input x: q = W_q x, laid out head by head as [``dim`` unrotated ;
 ``kv_rank + rot_dim`` rows, the first kv_rank RMS-normed (plain weight) are the latent c, the last rot_dim, rotated,
 are a key part r that all heads share.  Head j's key is [W_uk_j c ; r] and its value W_uv_j c; causal softmax with
 the given scale; the heads' outputs are optionally multiplied by sigmoid(W_g x), element by element (``gate=True``) or
-with one gate per head (``gate="head"``, W_g has ``heads`` rows), then projected by W_o.  With ``q_rank`` the queries
-go through a latent of their own: c_q = RMSnorm(W_dq x) (plain weight), q = W_uq c_q.
+with one gate per head (``gate="head"``, W_g has ``heads`` rows), then projected by W_o.  With ``q_rank`` the queries are
+made in two steps: the rows W_dq x of that width, RMS-normed and multiplied by a weight, then W_uq on the result.
 
 Only c and r are cached (one row of kv_rank + rot_dim elements per token: a cache group with one key head and no
 values).  The queries are folded through W_uk (a_j = W_uk_j^T q_j, one batched product), attention runs over the

@@ -18,8 +18,8 @@ pairs of one product.
 ``identity`` = n > 0: the router has ``experts`` + n outputs, and the last n stand for experts without tensors whose
 output is their input (times the weight).  ``correction``: a tensor of one number per router output that is added to the
 scores for the choice only; the weights are made from the scores themselves.  ``groups`` = (count, keep): the router's
-outputs (identity ones included) form ``count`` equal groups of neighbours, a group's score is its largest choice score,
-and only members of the best ``keep`` groups can be chosen.
+outputs (identity ones included) are cut into ``count`` equal runs of adjacent ones, a run is ranked by the best corrected
+score in it, and only members of the ``keep`` best runs are eligible.
 
 The pairs (token, choice) are sorted by expert on the device and both products run over the sorted rows
 (csrc/moe.cu); no count comes back to the host, so a step with this part may be captured.

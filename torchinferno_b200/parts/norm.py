@@ -78,7 +78,7 @@ class LayerNorm(Norm):
 
 
 class TanhNorm(Norm):
-    """y = tanh(alpha * x) * w + b: a norm without mean or variance ("dynamic tanh"); ``alpha`` is a learned scalar,
+    """y = tanh(alpha * x) * w + b: a norm that takes no statistic of the row ("dynamic tanh"); ``alpha`` is a learned scalar,
     stored as a tensor without dimensions.  All of it in fp32 (csrc/hyper_streams.cu: it is the read of a residual in
     streams, with one stream here).  ``bias_name`` / ``alpha_name`` default to the weight's name with ``.b`` / ``.alpha``."""
 
